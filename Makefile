@@ -1,0 +1,52 @@
+# Builds libuccl.so (host runtime + sm_100a kernels), the pybind11 module and the sample
+# network plugin, all in-tree.  `make -j` is what __graft_entry__.build() runs.
+CUDA_HOME ?= /usr/local/cuda
+NVCC      ?= $(CUDA_HOME)/bin/nvcc
+CXX       ?= g++
+PYTHON    ?= python3
+
+PYINC     := $(shell $(PYTHON) -c "import sysconfig; print(sysconfig.get_paths()['include'])")
+PYBINDINC := $(shell $(PYTHON) -c "import pybind11; print(pybind11.get_include())")
+EXTSUFFIX := $(shell $(PYTHON) -c "import sysconfig; print(sysconfig.get_config_var('EXT_SUFFIX'))")
+
+BUILD     := build
+PKG       := unified_ccl_b200
+INCLUDES  := -Iinclude -Icsrc -I$(CUDA_HOME)/include
+CXXFLAGS  := -O2 -g -std=c++17 -fPIC -Wall -Wno-unused-function -pthread $(INCLUDES)
+NVFLAGS   := -O3 -std=c++17 -lineinfo -gencode arch=compute_100a,code=sm_100a \
+             -Xcompiler -fPIC,-Wall,-Wno-unused-function --expt-relaxed-constexpr $(INCLUDES)
+LDFLAGS   := -shared -L$(CUDA_HOME)/lib64 -lcudart_static -ldl -lpthread -lrt
+
+CC_SRCS := $(wildcard csrc/core/*.cc csrc/mem/*.cc csrc/transport/*.cc csrc/protocols/*.cc \
+             csrc/rma/*.cc csrc/host/*.cc)
+CU_SRCS := $(wildcard csrc/kernels/*.cu)
+CC_OBJS := $(patsubst %.cc,$(BUILD)/%.o,$(CC_SRCS))
+CU_OBJS := $(patsubst %.cu,$(BUILD)/%.cu.o,$(CU_SRCS))
+
+LIB     := $(PKG)/libuccl.so
+PYMOD   := $(PKG)/_uccl_bindings$(EXTSUFFIX)
+PLUGIN  := plugins/sample/libuccl-net-sample.so
+
+all: $(LIB) $(PYMOD) $(PLUGIN)
+
+$(BUILD)/%.o: %.cc $(wildcard include/*.h csrc/*/*.h)
+	@mkdir -p $(dir $@)
+	$(CXX) $(CXXFLAGS) -c $< -o $@
+
+$(BUILD)/%.cu.o: %.cu $(wildcard include/*.h csrc/*/*.h csrc/kernels/*.cuh)
+	@mkdir -p $(dir $@)
+	$(NVCC) $(NVFLAGS) -c $< -o $@
+
+$(LIB): $(CC_OBJS) $(CU_OBJS)
+	$(CXX) -o $@ $^ $(LDFLAGS)
+
+$(PYMOD): csrc/python/bindings.cc $(LIB) $(wildcard include/*.h)
+	$(CXX) $(CXXFLAGS) -fvisibility=hidden -I$(PYINC) -I$(PYBINDINC) -shared $< -o $@ \
+
+$(PLUGIN): plugins/sample/plugin.cc include/uccl_net.h include/uccl.h
+	$(CXX) $(CXXFLAGS) -shared $< -o $@
+
+clean:
+	rm -rf $(BUILD) $(LIB) $(PYMOD) $(PLUGIN)
+
+.PHONY: all clean

@@ -1,0 +1,429 @@
+// Persistent warp-specialised bf16 GEMM for sm_100a: C[M,N] = A[M,K] * B[N,K]^T (both K-major,
+// i.e. the torch.nn.Linear layout), fp32 accumulation in TMEM.
+//
+//   warp 0      TMA producer : streams 128x64 A tiles and 256x64 B tiles (two 128-row boxes)
+//                              through a 4-stage shared-memory ring, 128-byte swizzle
+//   warp 1      MMA issuer   : one elected lane issues tcgen05.mma 128x256x16, accumulators
+//                              double-buffered in TMEM (2 x 256 columns) so the epilogue of
+//                              tile i overlaps the main loop of tile i+1
+//   warps 2..5  epilogue     : tcgen05.ld TMEM -> registers -> bf16 -> global
+//   CTAs >= gemm_ctas        : optional communication role (all-gather push of A rows, or
+//                              reduce-scatter pull of finished C row blocks) running in the same
+//                              launch so that NVLink traffic overlaps the math tile by tile
+//
+// The reference has no GEMM at all (its device code is limited to copy/reduce loops,
+// src/device/primitives.hpp:31-179); this kernel exists because the tensor-parallel fused
+// paths (all-gather -> GEMM, GEMM -> reduce-scatter) need a GEMM whose producer can wait on
+// per-row-block arrival flags and whose epilogue can publish per-row-block completion.
+//
+// Every wait is bounded: on expiry the CTA sets a shared bail word, records an error code in
+// *args.err, releases TMEM and returns.
+#pragma once
+#include <cuda.h>
+#include "ptx.cuh"
+
+namespace uccl {
+namespace gemm {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int STAGES = 4;
+constexpr int UMMA_K = 16;
+constexpr int A_STAGE_BYTES = BM * BK * 2;         // 16 KiB
+constexpr int B_STAGE_BYTES = BN * BK * 2;         // 32 KiB
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+
+enum Epilogue : int {
+  kEpiStore = 0,   // C[M,N] bf16
+  kEpiSwiGLU = 1,  // B rows of a tile are [128 gate rows | 128 up rows]; C[M,N/2] = silu(g)*u
+};
+
+enum CommRole : int {
+  kCommNone = 0,
+  kCommAllGatherPush = 1,   // extra CTAs broadcast this rank's A rows to all peers
+  kCommReduceScatter = 2,   // extra CTAs reduce finished row blocks of C across ranks
+};
+
+constexpr int kMaxPeers = 16;
+
+struct CommArgs {
+  int rank = 0;
+  int nranks = 1;
+  int use_multimem = 0;
+  uint32_t epoch = 1;             // value that flags/counters reach in this launch
+  uint64_t timeout_ns = 0;        // deadline for cross-rank waits
+  uint32_t* abort_flag = nullptr; // comm-wide abort word (device-visible)
+  // --- all-gather push: A_full is a symmetric buffer [M, K]; rows [rank*rows_per_rank, ...)
+  //     of the local copy already hold this rank's shard (or a_local points at it).
+  const void* a_local = nullptr;        // this rank's shard [rows_per_rank, K]
+  void* a_full_peer[kMaxPeers] = {};    // every rank's A_full (peer-mapped)
+  void* a_full_mc = nullptr;            // multicast alias of A_full (NVLS) or nullptr
+  uint32_t* ready_peer[kMaxPeers] = {}; // every rank's arrival flags [tiles_m]
+  int rows_per_rank = 0;
+  // --- reduce-scatter: C_partial is symmetric [M, N]; rank r owns rows [r*rows_per_rank,...)
+  const void* c_part_peer[kMaxPeers] = {};
+  const void* c_part_mc = nullptr;
+  uint32_t* done_peer[kMaxPeers] = {};  // every rank's completion counters [tiles_m]
+  void* rs_out = nullptr;               // [rows_per_rank, N] bf16
+  int rs_ldo = 0;
+};
+
+struct Args {
+  int M, N, K;
+  __nv_bfloat16* C;
+  int ldc;
+  int tiles_m, tiles_n;
+  int gemm_ctas;            // CTAs [0, gemm_ctas) run the GEMM roles
+  int m_rot;                // row-block rotation: logical block i maps to (i + m_rot) % tiles_m
+  int b_half_rows;          // SwiGLU: row offset of the "up" half inside B; plain: unused
+  const uint32_t* a_ready;  // optional arrival flags per row block (local memory)
+  uint32_t a_ready_target;
+  int a_local_lo, a_local_hi;   // row blocks in [lo, hi) need no wait
+  uint32_t* err;            // error word (mapped or device memory); 0 = ok
+  CommArgs comm;
+};
+
+__device__ __forceinline__ void tile_coords(const Args& a, int tile, int& mb, int& nb) {
+  constexpr int GROUP_M = 16;
+  const int per_group = GROUP_M * a.tiles_n;
+  const int g = tile / per_group;
+  const int first = g * GROUP_M;
+  const int gsz = min(GROUP_M, a.tiles_m - first);
+  const int r = tile - g * per_group;
+  int m = first + (r % gsz);
+  nb = r / gsz;
+  m += a.m_rot;
+  if (m >= a.tiles_m) m -= a.tiles_m;
+  mb = m;
+}
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
+
+// Bounded wait until *flag >= target. Returns false on timeout / abort.
+__device__ __forceinline__ bool wait_flag_geq(const uint32_t* flag, uint32_t target,
+                                              uint64_t timeout_ns, const uint32_t* abort_flag) {
+  if (ptx::ld_acquire_sys_u32(flag) >= target) return true;
+  const uint64_t t0 = ptx::globaltimer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    if (ptx::ld_acquire_sys_u32(flag) >= target) return true;
+    if ((++spins & 63u) == 0) {
+      if (abort_flag && ptx::ld_relaxed_sys_u32(abort_flag)) return false;
+      if (timeout_ns && ptx::globaltimer_ns() - t0 > timeout_ns) return false;
+    }
+    __nanosleep(64);
+  }
+}
+
+// ------------------------------------------------------------------ communication roles
+// All-gather push: the extra CTAs copy this rank's A shard into every peer's A_full (one
+// multimem.st per 16 bytes when NVLS is available, else one store per peer), one row block at a
+// time, and raise that row block's arrival flag on every peer afterwards.
+__device__ void comm_allgather_push(const Args& a, int cta, int nctas) {
+  const CommArgs& c = a.comm;
+  const int blocks = (c.rows_per_rank + BM - 1) / BM;
+  const size_t row_bytes = static_cast<size_t>(a.K) * 2;
+  const size_t shard_off = static_cast<size_t>(c.rank) * c.rows_per_rank * row_bytes;
+  const int first_blk = (c.rank * c.rows_per_rank) / BM;
+  for (int b = cta; b < blocks; b += nctas) {
+    const int rows = min(BM, c.rows_per_rank - b * BM);
+    const size_t off = static_cast<size_t>(b) * BM * row_bytes;
+    const size_t n16 = static_cast<size_t>(rows) * row_bytes / 16;
+    const char* src = static_cast<const char*>(c.a_local) + off;
+    if (c.use_multimem) {
+      char* dst = static_cast<char*>(c.a_full_mc) + shard_off + off;
+      for (size_t i = threadIdx.x; i < n16; i += blockDim.x)
+        ptx::multimem_st_v4(dst + i * 16, ptx::ld_global_v4(src + i * 16));
+    } else {
+      for (size_t i = threadIdx.x; i < n16; i += blockDim.x) {
+        const uint4 v = ptx::ld_global_v4(src + i * 16);
+        for (int p = 0; p < c.nranks; ++p) {
+          const int peer = (c.rank + p) % c.nranks;
+          ptx::st_global_v4(static_cast<char*>(c.a_full_peer[peer]) + shard_off + off + i * 16, v);
+        }
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x < static_cast<unsigned>(c.nranks)) {
+      ptx::fence_sys();
+      ptx::st_release_sys_u32(c.ready_peer[threadIdx.x] + first_blk + b, c.epoch);
+    }
+    __syncthreads();
+  }
+}
+
+// Reduce-scatter pull: once every rank has finished all column tiles of one of my row blocks
+// (done counter == nranks * tiles_n * 4 * epoch), sum the nranks partial copies (in-switch with
+// multimem.ld_reduce, else peer loads with fp32 accumulation) and write bf16 to rs_out.
+__device__ void comm_reduce_scatter(const Args& a, int cta, int nctas) {
+  const CommArgs& c = a.comm;
+  const int blocks = (c.rows_per_rank + BM - 1) / BM;
+  const int first_blk = (c.rank * c.rows_per_rank) / BM;
+  const size_t row_bytes = static_cast<size_t>(a.N) * 2;
+  const uint32_t target = c.epoch * static_cast<uint32_t>(c.nranks * a.tiles_n * 4);
+  for (int b = cta; b < blocks; b += nctas) {
+    __shared__ int ok_s;
+    if (threadIdx.x == 0) {
+      const bool ok = wait_flag_geq(c.done_peer[c.rank] + first_blk + b, target, c.timeout_ns,
+                                    c.abort_flag);
+      if (!ok && a.err) atomicCAS(a.err, 0u, 0x52530000u | static_cast<uint32_t>(b));
+      ok_s = ok ? 1 : 0;
+    }
+    __syncthreads();
+    const int ok = ok_s;
+    __syncthreads();
+    if (!ok) return;
+    const int rows = min(BM, c.rows_per_rank - b * BM);
+    const size_t src_off = (static_cast<size_t>(c.rank) * c.rows_per_rank + b * BM) * row_bytes;
+    const size_t per_row16 = row_bytes / 16;
+    const size_t n16 = static_cast<size_t>(rows) * per_row16;
+    for (size_t i = threadIdx.x; i < n16; i += blockDim.x) {
+      const size_t r = i / per_row16, col16 = i - r * per_row16;
+      uint4 out;
+      if (c.use_multimem) {
+        out = ptx::multimem_ld_reduce_bf16x8(static_cast<const char*>(c.c_part_mc) + src_off + i * 16);
+      } else {
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int p = 0; p < c.nranks; ++p) {
+          const int peer = (c.rank + p) % c.nranks;
+          const uint4 v = ptx::ld_stream_v4(static_cast<const char*>(c.c_part_peer[peer]) + src_off + i * 16);
+          const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = ptx::unpack_bf16x2(w[j]);
+            acc[2 * j] += f.x;
+            acc[2 * j + 1] += f.y;
+          }
+        }
+        out.x = ptx::pack_bf16x2(acc[0], acc[1]);
+        out.y = ptx::pack_bf16x2(acc[2], acc[3]);
+        out.z = ptx::pack_bf16x2(acc[4], acc[5]);
+        out.w = ptx::pack_bf16x2(acc[6], acc[7]);
+      }
+      char* dst = static_cast<char*>(c.rs_out) +
+                  (static_cast<size_t>(b) * BM + r) * static_cast<size_t>(c.rs_ldo) * 2 + col16 * 16;
+      ptx::st_global_v4(dst, out);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ the kernel
+template <int EPI, int COMM>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const Args a) {
+  if (COMM != kCommNone && static_cast<int>(blockIdx.x) >= a.gemm_ctas) {
+    const int cta = blockIdx.x - a.gemm_ctas;
+    const int nctas = gridDim.x - a.gemm_ctas;
+    if (COMM == kCommAllGatherPush) comm_allgather_push(a, cta, nctas);
+    if (COMM == kCommReduceScatter) comm_reduce_scatter(a, cta, nctas);
+    return;
+  }
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* full_bar = bars;                   // [STAGES]
+  uint64_t* empty_bar = bars + STAGES;         // [STAGES]
+  uint64_t* tfull_bar = bars + 2 * STAGES;     // [2]
+  uint64_t* tempty_bar = bars + 2 * STAGES + 2;  // [2]
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile uint32_t* bail = tmem_holder + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = a.tiles_m * a.tiles_n;
+  const int num_kb = (a.K + BK - 1) / BK;
+  const int gemm_ctas = (COMM != kCommNone) ? a.gemm_ctas : gridDim.x;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(&full_bar[s], 1);
+      ptx::mbar_init(&empty_bar[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(&tfull_bar[i], 1);
+      ptx::mbar_init(&tempty_bar[i], 4);  // one arrive per epilogue warp
+    }
+    *bail = 0;
+    ptx::mbar_fence_init();
+    ptx::prefetch_tmap(&tmA);
+    ptx::prefetch_tmap(&tmB);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(tmem_holder, TMEM_COLS);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && !*bail; tile += gemm_ctas) {
+        int mb, nb;
+        tile_coords(a, tile, mb, nb);
+        if (a.a_ready && !(mb >= a.a_local_lo && mb < a.a_local_hi)) {
+          if (!wait_flag_geq(a.a_ready + mb, a.a_ready_target, a.comm.timeout_ns, a.comm.abort_flag)) {
+            if (a.err) atomicCAS(a.err, 0u, 0x41470000u | static_cast<uint32_t>(mb));
+            *bail = 1;
+            break;
+          }
+          // data was written by peers through the generic proxy; TMA reads via the async proxy
+          ptx::fence_proxy_async();
+        }
+        const int m0 = mb * BM;
+        int brow0, brow1;
+        if (EPI == kEpiSwiGLU) {
+          brow0 = nb * (BN / 2);
+          brow1 = a.b_half_rows + nb * (BN / 2);
+        } else {
+          brow0 = nb * BN;
+          brow1 = nb * BN + BN / 2;
+        }
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!ptx::mbar_wait_bounded(&empty_bar[s], ph ^ 1, bail)) break;
+          uint8_t* sA = smem + s * STAGE_BYTES;
+          uint8_t* sB = sA + A_STAGE_BYTES;
+          ptx::mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+          ptx::tma_load_2d(sA, &tmA, &full_bar[s], kb * BK, m0);
+          ptx::tma_load_2d(sB, &tmB, &full_bar[s], kb * BK, brow0);
+          ptx::tma_load_2d(sB + B_STAGE_BYTES / 2, &tmB, &full_bar[s], kb * BK, brow1);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = ptx::umma_idesc_f16(1u, BM, BN);
+      uint32_t it = 0, tcount = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && !*bail; tile += gemm_ctas, ++tcount) {
+        const uint32_t acc = tcount & 1, acc_ph = (tcount >> 1) & 1;
+        if (!ptx::mbar_wait_bounded(&tempty_bar[acc], acc_ph ^ 1, bail)) break;
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!ptx::mbar_wait_bounded(&full_bar[s], ph, bail)) break;
+          ptx::tc_fence_after();
+          const uint32_t sA = ptx::smem_u32(smem + s * STAGE_BYTES);
+          const uint64_t da = ptx::umma_smem_desc_sw128(sA);
+          const uint64_t db = ptx::umma_smem_desc_sw128(sA + A_STAGE_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t koff = static_cast<uint64_t>((k * UMMA_K * 2) >> 4);
+            ptx::umma_f16(d_tmem, da + koff, db + koff, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          ptx::umma_commit(&empty_bar[s]);
+        }
+        ptx::umma_commit(&tfull_bar[acc]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue warps
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    uint32_t tcount = 0;
+    for (int tile = blockIdx.x; tile < num_tiles && !*bail; tile += gemm_ctas, ++tcount) {
+      int mb, nb;
+      tile_coords(a, tile, mb, nb);
+      const uint32_t acc = tcount & 1, acc_ph = (tcount >> 1) & 1;
+      if (!ptx::mbar_wait_bounded(&tfull_bar[acc], acc_ph, bail)) break;
+      ptx::tc_fence_after();
+      const int row = mb * BM + q * 32 + lane;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+      if (EPI == kEpiStore) {
+        __nv_bfloat16* crow = a.C + static_cast<size_t>(row) * a.ldc + static_cast<size_t>(nb) * BN;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          ptx::tmem_ld_32x32b_x32(taddr + c * 32, r);
+          ptx::tmem_ld_wait();
+          const int col0 = nb * BN + c * 32;
+          if (row < a.M) {
+            if (col0 + 32 <= a.N) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint4 v;
+                v.x = ptx::pack_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+                v.y = ptx::pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+                v.z = ptx::pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+                v.w = ptx::pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+                *reinterpret_cast<uint4*>(crow + c * 32 + j * 8) = v;
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < a.N) crow[c * 32 + j] = __float2bfloat16(__uint_as_float(r[j]));
+            }
+          }
+        }
+      } else {
+        // gate columns [0,128) and up columns [128,256) of the accumulator
+        const int out_n = a.N / 2;
+        __nv_bfloat16* crow = a.C + static_cast<size_t>(row) * a.ldc + static_cast<size_t>(nb) * (BN / 2);
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          uint32_t g[32], u[32];
+          ptx::tmem_ld_32x32b_x32(taddr + c * 32, g);
+          ptx::tmem_ld_32x32b_x32(taddr + BN / 2 + c * 32, u);
+          ptx::tmem_ld_wait();
+          const int col0 = nb * (BN / 2) + c * 32;
+          if (row < a.M) {
+            if (col0 + 32 <= out_n) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float h[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                  h[e] = silu_f(__uint_as_float(g[8 * j + e])) * __uint_as_float(u[8 * j + e]);
+                uint4 v;
+                v.x = ptx::pack_bf16x2(h[0], h[1]);
+                v.y = ptx::pack_bf16x2(h[2], h[3]);
+                v.z = ptx::pack_bf16x2(h[4], h[5]);
+                v.w = ptx::pack_bf16x2(h[6], h[7]);
+                *reinterpret_cast<uint4*>(crow + c * 32 + j * 8) = v;
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < out_n)
+                  crow[c * 32 + j] = __float2bfloat16(silu_f(__uint_as_float(g[j])) * __uint_as_float(u[j]));
+            }
+          }
+        }
+      }
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&tempty_bar[acc]);
+      if (COMM == kCommReduceScatter) {
+        // Publish: this warp's 32 rows x BN columns of row block mb are in memory. Each of
+        // the four epilogue warps adds 1 to the owner's counter for that row block, so the
+        // owner expects nranks * tiles_n * 4 per launch. No cross-warp barrier is needed.
+        if (lane == 0) {
+          ptx::fence_sys();
+          const int owner = min((mb * BM) / a.comm.rows_per_rank, a.comm.nranks - 1);
+          ptx::red_release_sys_add_u32(a.comm.done_peer[owner] + mb, 1u);
+        }
+      }
+    }
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && *bail && a.err) atomicCAS(a.err, 0u, 0x47454d4du);
+}
+
+}  // namespace gemm
+}  // namespace uccl

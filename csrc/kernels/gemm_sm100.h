@@ -1,0 +1,51 @@
+// Host-side launcher interface of the tcgen05 GEMM (see gemm_sm100.cuh for the kernel).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "uccl.h"
+
+namespace uccl {
+
+struct GemmCommPlan;  // defined in gemm_sm100.cu next to the kernel argument structs
+
+struct GemmLaunch {
+  const void* A = nullptr;  // [M, K] bf16, row stride lda
+  const void* B = nullptr;  // [N, K] bf16, row stride ldb
+  void* C = nullptr;        // [M, N] (or [M, N/2] for SwiGLU) bf16, row stride ldc
+  int M = 0, N = 0, K = 0;
+  int lda = 0, ldb = 0, ldc = 0;
+  int epilogue = 0;         // 0 store, 1 SwiGLU
+  int max_ctas = 0;         // 0 = one per SM
+  uint32_t* err = nullptr;  // optional device-visible error word
+};
+
+// Fusion descriptor filled by the tensor-parallel entry points.
+struct GemmFusion {
+  int role = 0;  // 0 none, 1 all-gather push, 2 reduce-scatter
+  int rank = 0, nranks = 1;
+  int comm_ctas = 0;
+  int use_multimem = 0;
+  uint32_t epoch = 1;
+  uint64_t timeout_ns = 0;
+  uint32_t* abort_flag = nullptr;
+  int rows_per_rank = 0;
+  // all-gather
+  const void* a_local = nullptr;
+  void* a_full_peer[UCCL_MAX_LOCAL_RANKS] = {};
+  void* a_full_mc = nullptr;
+  uint32_t* ready_peer[UCCL_MAX_LOCAL_RANKS] = {};
+  // reduce-scatter
+  const void* c_part_peer[UCCL_MAX_LOCAL_RANKS] = {};
+  const void* c_part_mc = nullptr;
+  uint32_t* done_peer[UCCL_MAX_LOCAL_RANKS] = {};
+  void* rs_out = nullptr;
+  int rs_ldo = 0;
+};
+
+ucclResult_t launchGemmBf16(const GemmLaunch& g, const GemmFusion* fusion, cudaStream_t stream);
+
+// Number of SMs of the current device (cached per device).
+int deviceSmCount();
+
+}  // namespace uccl

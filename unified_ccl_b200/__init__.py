@@ -1,0 +1,19 @@
+"""Blackwell-native unified collective communication library (Python side).
+
+The native code lives in ``libuccl.so`` (host runtime + sm_100a kernels) and the pybind11
+module ``_uccl_bindings`` next to this file; both are built in-tree by ``make`` (or
+``python -c "import __graft_entry__ as g; g.build()"``).  Importing this package never
+falls back to a pure-Python implementation: if the extension is missing the import fails
+with the build command in the message.
+"""
+import os as _os
+
+try:
+    from . import _uccl_bindings as _C  # noqa: F401
+except ImportError as _e:  # pragma: no cover - exercised only on a broken checkout
+    raise ImportError(
+        "unified_ccl_b200: native extension not built; run `make -j` in "
+        f"{_os.path.dirname(_os.path.dirname(_os.path.abspath(__file__)))} ({_e})"
+    ) from _e
+
+__version__ = "0.1.0"
