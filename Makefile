@@ -42,6 +42,7 @@ $(LIB): $(CC_OBJS) $(CU_OBJS)
 
 $(PYMOD): csrc/python/bindings.cc $(LIB) $(wildcard include/*.h)
 	$(CXX) $(CXXFLAGS) -fvisibility=hidden -I$(PYINC) -I$(PYBINDINC) -shared $< -o $@ \
+	    -L$(PKG) -luccl -Wl,-rpath,'$$ORIGIN'
 
 $(PLUGIN): plugins/sample/plugin.cc include/uccl_net.h include/uccl.h
 	$(CXX) $(CXXFLAGS) -shared $< -o $@

@@ -1,0 +1,435 @@
+// NVLink-domain collectives as single persistent kernels: one-shot, two-shot, NVLS (multimem)
+// and low-latency all-reduce; pull / push all-gather; pull reduce-scatter; broadcast; reduce;
+// all-to-all.
+//
+// Mapping to the reference: one-shot replaces src/algorithms/one_shot.cc:21-88, the symmetric
+// pull kernels replace src/algorithms/symmetric.cc:23-278 (which have no cross-rank
+// synchronisation and make every work-group redo the whole buffer), "channels" are the CTAs of
+// one launch instead of one single-work-group launch per channel (src/enqueue.cc:216-231), and
+// sums are carried in fp32 (the reference adds in the 16-bit type, src/device/reduce_kernel.hpp:19).
+//
+// Common shape of every kernel:
+//   [copy user input into the local work buffer]  -> rank barrier (peers' inputs are ready)
+//   -> remote loads / stores / multimem ops        -> rank barrier (peers are done with my memory)
+//   -> [copy the local work buffer out to the user's buffer]
+// Work buffers are 16-byte aligned and padded to whole 16-byte vectors by the host side, so the
+// inner loops only ever move uint4.
+#include "collectives.cuh"
+
+#include "coll_device.cuh"
+
+namespace uccl {
+namespace dev {
+
+// slice `b` of `B` of the byte range [0, bytes), in whole 16-byte vectors (bytes % 16 == 0)
+__device__ __forceinline__ void slice16(size_t bytes, int B, int b, size_t* off, size_t* len) {
+  size_t o, l;
+  split(bytes >> 4, B, b, &o, &l);
+  *off = o << 4;
+  *len = l << 4;
+}
+// slice of an arbitrary byte range: vectors are spread over CTAs, the last CTA takes the tail
+__device__ __forceinline__ void slice_bytes(size_t bytes, int B, int b, size_t* off, size_t* len) {
+  slice16(bytes & ~size_t(15), B, b, off, len);
+  if (b == B - 1) *len += bytes & 15;
+}
+
+// copy [begin, begin+len) of a padded range, but never past the exact user length
+__device__ __forceinline__ void copy_clamped(char* dstBase, const char* srcBase, size_t begin, size_t len,
+                                             size_t userBytes) {
+  if (begin >= userBytes) return;
+  block_copy(dstBase + begin, srcBase + begin, min(len, userBytes - begin));
+}
+
+template <int DT>
+__device__ __forceinline__ uint4 reduce_peers(const CollArgs& a, size_t byteOff) {
+  using V = Vec<DT>;
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  const int n = a.dc.nranks;
+  uint4 v[UCCL_MAX_LOCAL_RANKS > 8 ? 8 : UCCL_MAX_LOCAL_RANKS];
+  for (int p0 = 0; p0 < n; p0 += 8) {
+    const int m = min(8, n - p0);
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (j < m) v[j] = ptx::ld_stream_v4(a.in[(a.dc.rank + p0 + j) % n] + byteOff);
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (j < m) V::add(acc, v[j]);
+  }
+  return V::pack(acc);
+}
+
+// ------------------------------------------------------------------ all-reduce, one-shot
+template <int DT>
+__device__ void ar_oneshot(const CollArgs& a) {
+  const DevComm& dc = a.dc;
+  const int B = gridDim.x, b = blockIdx.x;
+  size_t off, len;
+  slice16(a.bytes, B, b, &off, &len);
+  if (a.inUser) copy_clamped(const_cast<char*>(a.in[dc.rank]), a.inUser, off, len, a.userBytes);
+  if (!rank_barrier(dc)) return;
+  char* dst = a.out[dc.rank];
+  for (size_t i = off + (static_cast<size_t>(threadIdx.x) << 4); i < off + len; i += static_cast<size_t>(blockDim.x) << 4)
+    st_out16(dst + i, reduce_peers<DT>(a, i));
+  if (!rank_barrier(dc)) return;
+  if (a.outUser) copy_clamped(a.outUser, dst, off, len, a.userBytes);
+}
+
+// ------------------------------------------------------------------ all-reduce, two-shot / NVLS
+// Block b owns slice b of every rank's shard for the copies, and slice b of its own rank's
+// shard for the reduction, so that the CTA-level barrier with CTA b of each peer covers exactly
+// the data it depends on.
+template <int DT, bool NVLS>
+__device__ void ar_twoshot(const CollArgs& a) {
+  using V = Vec<DT>;
+  const DevComm& dc = a.dc;
+  const int B = gridDim.x, b = blockIdx.x, n = dc.nranks;
+  const size_t nvec = a.bytes >> 4;
+  if (a.inUser) {
+    for (int s = 0; s < n; ++s) {
+      size_t so, sl, o, l;
+      split(nvec, n, s, &so, &sl);
+      split(sl, B, b, &o, &l);
+      copy_clamped(const_cast<char*>(a.in[dc.rank]), a.inUser, (so + o) << 4, l << 4, a.userBytes);
+    }
+  }
+  if (!rank_barrier(dc)) return;
+  {
+    size_t so, sl, o, l;
+    split(nvec, n, dc.rank, &so, &sl);
+    split(sl, B, b, &o, &l);
+    const size_t begin = (so + o) << 4, end = (so + o + l) << 4;
+    const size_t stride = static_cast<size_t>(blockDim.x) << 4;
+    if (NVLS) {
+      size_t i = begin + (static_cast<size_t>(threadIdx.x) << 4);
+      for (; i + 3 * stride < end; i += 4 * stride) {
+        const uint4 v0 = V::mc_reduce(a.inMc + i);
+        const uint4 v1 = V::mc_reduce(a.inMc + i + stride);
+        const uint4 v2 = V::mc_reduce(a.inMc + i + 2 * stride);
+        const uint4 v3 = V::mc_reduce(a.inMc + i + 3 * stride);
+        ptx::multimem_st_v4(a.outMc + i, v0);
+        ptx::multimem_st_v4(a.outMc + i + stride, v1);
+        ptx::multimem_st_v4(a.outMc + i + 2 * stride, v2);
+        ptx::multimem_st_v4(a.outMc + i + 3 * stride, v3);
+      }
+      for (; i < end; i += stride) ptx::multimem_st_v4(a.outMc + i, V::mc_reduce(a.inMc + i));
+    } else {
+      for (size_t i = begin + (static_cast<size_t>(threadIdx.x) << 4); i < end; i += stride) {
+        const uint4 v = reduce_peers<DT>(a, i);
+        for (int p = 0; p < n; ++p) ptx::st_global_v4(a.out[(dc.rank + p) % n] + i, v);
+      }
+    }
+  }
+  if (!rank_barrier(dc)) return;
+  if (a.outUser) {
+    for (int s = 0; s < n; ++s) {
+      size_t so, sl, o, l;
+      split(nvec, n, s, &so, &sl);
+      split(sl, B, b, &o, &l);
+      copy_clamped(a.outUser, a.out[dc.rank], (so + o) << 4, l << 4, a.userBytes);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ all-reduce, low latency
+// Every rank stores its data into a dedicated slot of every peer's arena as 16-byte packets
+// {data0, flag, data1, flag}; a packet is valid once both flags equal the CTA's epoch.  No barrier
+// and no prior knowledge of the peers' buffers is needed: one NVLink traversal end to end.
+// CTA b handles bytes [b * kLLDataPerBlock, ...).  Slots are double-buffered by epoch parity: a
+// rank can be at most one operation ahead of a peer, because finishing an operation requires
+// every peer's packets of that same operation.
+template <int DT>
+__device__ void ar_ll(const CollArgs& a) {
+  using V = Vec<DT>;
+  const DevComm& dc = a.dc;
+  const int b = blockIdx.x, n = dc.nranks, t = threadIdx.x;
+  const uint32_t e = dc.llEpochs[b] + 1;
+  const int parity = e & 1;
+  const size_t base = static_cast<size_t>(b) * kLLDataPerBlock;
+  const size_t valid = a.bytes > base ? min(static_cast<size_t>(kLLDataPerBlock), a.bytes - base) : 0;
+  const size_t unitOff = static_cast<size_t>(t) * 8;  // this thread's 8 data bytes
+  constexpr int EPU = 8 / V::ES;                      // elements per unit
+  float mine[EPU];
+  int nel = 0;
+  if (unitOff < valid) {
+    nel = static_cast<int>(min(static_cast<size_t>(8), valid - unitOff) / V::ES);
+    for (int j = 0; j < EPU; ++j) mine[j] = j < nel ? V::load1(a.inUser + base + unitOff + j * V::ES) : 0.f;
+    // pack my elements into two 32-bit words
+    uint32_t w0, w1;
+    if (DT == DT_F32) {
+      w0 = __float_as_uint(mine[0]);
+      w1 = __float_as_uint(mine[EPU - 1]);
+    } else if (DT == DT_BF16) {
+      w0 = ptx::pack_bf16x2(mine[0], mine[1 % EPU]);
+      w1 = ptx::pack_bf16x2(mine[2 % EPU], mine[3 % EPU]);
+    } else {
+      w0 = ptx::pack_f16x2(mine[0], mine[1 % EPU]);
+      w1 = ptx::pack_f16x2(mine[2 % EPU], mine[3 % EPU]);
+    }
+    const uint4 pkt = make_uint4(w0, e, w1, e);
+    const size_t slotOff = kArenaLLOff +
+                           ((static_cast<size_t>(parity) * kLLBlocks + b) * UCCL_MAX_LOCAL_RANKS + dc.rank) * kLLSlotBytes +
+                           static_cast<size_t>(t) * 16;
+    for (int p = 1; p < n; ++p) ptx::st_volatile_v4(dc.arena[(dc.rank + p) % n] + slotOff, pkt);
+  }
+  bool ok = true;
+  if (unitOff < valid) {
+    float acc[EPU];
+    for (int j = 0; j < EPU; ++j) acc[j] = mine[j];
+    const uint64_t t0 = ptx::globaltimer_ns();
+    for (int p = 1; p < n && ok; ++p) {
+      const int peer = (dc.rank + p) % n;
+      const char* slot = dc.arena[dc.rank] + kArenaLLOff +
+                         ((static_cast<size_t>(parity) * kLLBlocks + b) * UCCL_MAX_LOCAL_RANKS + peer) * kLLSlotBytes +
+                         static_cast<size_t>(t) * 16;
+      uint4 pkt;
+      uint32_t spins = 0;
+      while (true) {
+        pkt = ptx::ld_volatile_v4(slot);
+        if (pkt.y == e && pkt.w == e) break;
+        if ((++spins & 63u) == 0) {
+          if (aborted(dc)) { ok = false; break; }
+          if (ptx::globaltimer_ns() - t0 > dc.timeoutNs) {
+            record_status(dc, DEV_TIMEOUT_LL, peer, e);
+            ok = false;
+            break;
+          }
+        }
+      }
+      if (!ok) break;
+      if (DT == DT_F32) {
+        acc[0] += __uint_as_float(pkt.x);
+        acc[EPU - 1] += (EPU > 1) ? __uint_as_float(pkt.z) : 0.f;
+      } else if (DT == DT_BF16) {
+        const float2 f0 = ptx::unpack_bf16x2(pkt.x), f1 = ptx::unpack_bf16x2(pkt.z);
+        acc[0] += f0.x; acc[1 % EPU] += f0.y; acc[2 % EPU] += f1.x; acc[3 % EPU] += f1.y;
+      } else {
+        const float2 f0 = ptx::unpack_f16x2(pkt.x), f1 = ptx::unpack_f16x2(pkt.z);
+        acc[0] += f0.x; acc[1 % EPU] += f0.y; acc[2 % EPU] += f1.x; acc[3 % EPU] += f1.y;
+      }
+    }
+    if (ok)
+      for (int j = 0; j < nel; ++j) V::store1(a.outUser + base + unitOff + j * V::ES, acc[j]);
+  }
+  __syncthreads();
+  if (t == 0) dc.llEpochs[b] = e;
+}
+
+// ------------------------------------------------------------------ all-gather
+// pull: every rank reads each peer's chunk straight into its own output
+__device__ void ag_pull(const CollArgs& a) {
+  const DevComm& dc = a.dc;
+  const int B = gridDim.x, b = blockIdx.x, n = dc.nranks;
+  size_t off, len;
+  slice_bytes(a.chunkBytes, B, b, &off, &len);
+  if (a.inUser) block_copy(const_cast<char*>(a.in[dc.rank]) + off, a.inUser + off, len);
+  if (!rank_barrier(dc)) return;
+  for (int p = 0; p < n; ++p) {
+    const int peer = (dc.rank + p) % n;
+    block_copy(a.outUser + static_cast<size_t>(peer) * a.outStride + off, a.in[peer] + off, len);
+  }
+  rank_barrier(dc);
+}
+
+// push: every rank writes its chunk into slot [rank] of each peer's output (multimem.st
+// reaches all of them with one store when the output has a multicast alias)
+__device__ void ag_push(const CollArgs& a) {
+  const DevComm& dc = a.dc;
+  const int B = gridDim.x, b = blockIdx.x, n = dc.nranks;
+  size_t off, len;
+  slice16(a.chunkBytes, B, b, &off, &len);
+  if (!rank_barrier(dc)) return;  // peers are done with the previous contents of their output
+  const size_t dstOff = static_cast<size_t>(dc.rank) * a.outStride;
+  const size_t stride = static_cast<size_t>(blockDim.x) << 4;
+  if (a.outMc) {
+    size_t i = off + (static_cast<size_t>(threadIdx.x) << 4);
+    for (; i + 3 * stride < off + len; i += 4 * stride) {
+      const uint4 v0 = ptx::ld_global_v4(a.inUser + i), v1 = ptx::ld_global_v4(a.inUser + i + stride);
+      const uint4 v2 = ptx::ld_global_v4(a.inUser + i + 2 * stride), v3 = ptx::ld_global_v4(a.inUser + i + 3 * stride);
+      ptx::multimem_st_v4(a.outMc + dstOff + i, v0);
+      ptx::multimem_st_v4(a.outMc + dstOff + i + stride, v1);
+      ptx::multimem_st_v4(a.outMc + dstOff + i + 2 * stride, v2);
+      ptx::multimem_st_v4(a.outMc + dstOff + i + 3 * stride, v3);
+    }
+    for (; i < off + len; i += stride) ptx::multimem_st_v4(a.outMc + dstOff + i, ptx::ld_global_v4(a.inUser + i));
+  } else {
+    for (size_t i = off + (static_cast<size_t>(threadIdx.x) << 4); i < off + len; i += stride) {
+      const uint4 v = ptx::ld_global_v4(a.inUser + i);
+      for (int p = 0; p < n; ++p) ptx::st_global_v4(a.out[(dc.rank + p) % n] + dstOff + i, v);
+    }
+  }
+  rank_barrier(dc);
+}
+
+// ------------------------------------------------------------------ reduce-scatter (pull)
+template <int DT>
+__device__ void rs_pull(const CollArgs& a) {
+  using V = Vec<DT>;
+  const DevComm& dc = a.dc;
+  const int B = gridDim.x, b = blockIdx.x, n = dc.nranks;
+  size_t off, len;
+  slice16(a.chunkBytes, B, b, &off, &len);  // chunkBytes is padded to 16 by the host
+  if (a.inUser) {
+    // user chunks are inStride apart and exactly userBytes long; staged chunks are chunkBytes apart
+    for (int s = 0; s < n; ++s)
+      copy_clamped(const_cast<char*>(a.in[dc.rank]) + static_cast<size_t>(s) * a.chunkBytes,
+                   a.inUser + static_cast<size_t>(s) * a.inStride, off, len, a.userBytes);
+  }
+  if (!rank_barrier(dc)) return;
+  // inside the work buffers chunk s starts at s * workStride
+  const size_t workStride = a.inUser ? a.chunkBytes : a.inStride;
+  const size_t src = static_cast<size_t>(dc.rank) * workStride;
+  char* dst = a.out[dc.rank];
+  const size_t stride = static_cast<size_t>(blockDim.x) << 4;
+  if (a.inMc) {
+    size_t i = off + (static_cast<size_t>(threadIdx.x) << 4);
+    for (; i + 3 * stride < off + len; i += 4 * stride) {
+      const uint4 v0 = V::mc_reduce(a.inMc + src + i), v1 = V::mc_reduce(a.inMc + src + i + stride);
+      const uint4 v2 = V::mc_reduce(a.inMc + src + i + 2 * stride), v3 = V::mc_reduce(a.inMc + src + i + 3 * stride);
+      st_out16(dst + i, v0);
+      st_out16(dst + i + stride, v1);
+      st_out16(dst + i + 2 * stride, v2);
+      st_out16(dst + i + 3 * stride, v3);
+    }
+    for (; i < off + len; i += stride) st_out16(dst + i, V::mc_reduce(a.inMc + src + i));
+  } else {
+    for (size_t i = off + (static_cast<size_t>(threadIdx.x) << 4); i < off + len; i += stride)
+      st_out16(dst + i, reduce_peers<DT>(a, src + i));
+  }
+  if (!rank_barrier(dc)) return;
+  if (a.outUser) copy_clamped(a.outUser, dst, off, len, a.userBytes);
+}
+
+// ------------------------------------------------------------------ broadcast
+// pull: the root exposes its data (in place if symmetric, else through its staging area) and
+// every other rank copies it out with plain loads
+__device__ void bcast_pull(const CollArgs& a) {
+  const DevComm& dc = a.dc;
+  const int B = gridDim.x, b = blockIdx.x;
+  size_t off, len;
+  slice_bytes(a.userBytes, B, b, &off, &len);
+  const bool isRoot = dc.rank == a.root;
+  if (isRoot && a.inUser) block_copy(const_cast<char*>(a.in[dc.rank]) + off, a.inUser + off, len);
+  if (!rank_barrier(dc)) return;
+  if (!isRoot) {
+    block_copy(a.outUser + off, a.in[a.root] + off, len);
+  } else {
+    const char* src = a.inUser ? a.inUser : a.in[dc.rank];
+    if (a.outUser != src) block_copy(a.outUser + off, src + off, len);
+  }
+  rank_barrier(dc);
+}
+
+__device__ void bcast_push(const CollArgs& a) {
+  const DevComm& dc = a.dc;
+  const int B = gridDim.x, b = blockIdx.x, n = dc.nranks;
+  size_t off, len;
+  slice16(a.bytes, B, b, &off, &len);
+  if (!rank_barrier(dc)) return;
+  if (dc.rank == a.root) {
+    const size_t stride = static_cast<size_t>(blockDim.x) << 4;
+    for (size_t i = off + (static_cast<size_t>(threadIdx.x) << 4); i < off + len; i += stride) {
+      const uint4 v = ptx::ld_global_v4(a.inUser + i);
+      if (a.outMc) {
+        ptx::multimem_st_v4(a.outMc + i, v);
+      } else {
+        for (int p = 0; p < n; ++p) ptx::st_global_v4(a.out[(dc.rank + p) % n] + i, v);
+      }
+    }
+  }
+  rank_barrier(dc);
+}
+
+// ------------------------------------------------------------------ reduce (pull at the root)
+template <int DT>
+__device__ void reduce_pull(const CollArgs& a) {
+  using V = Vec<DT>;
+  const DevComm& dc = a.dc;
+  const int B = gridDim.x, b = blockIdx.x;
+  size_t off, len;
+  slice16(a.bytes, B, b, &off, &len);
+  if (a.inUser) copy_clamped(const_cast<char*>(a.in[dc.rank]), a.inUser, off, len, a.userBytes);
+  if (!rank_barrier(dc)) return;
+  char* dst = a.out[dc.rank];
+  if (dc.rank == a.root) {
+    const size_t stride = static_cast<size_t>(blockDim.x) << 4;
+    for (size_t i = off + (static_cast<size_t>(threadIdx.x) << 4); i < off + len; i += stride)
+      st_out16(dst + i, a.inMc ? V::mc_reduce(a.inMc + i) : reduce_peers<DT>(a, i));
+  }
+  if (!rank_barrier(dc)) return;
+  if (dc.rank == a.root && a.outUser) copy_clamped(a.outUser, dst, off, len, a.userBytes);
+}
+
+// ------------------------------------------------------------------ all-to-all (pull)
+__device__ void a2a_pull(const CollArgs& a) {
+  const DevComm& dc = a.dc;
+  const int B = gridDim.x, b = blockIdx.x, n = dc.nranks;
+  size_t off, len;
+  slice_bytes(a.chunkBytes, B, b, &off, &len);
+  const size_t workStride = a.inUser ? ((a.chunkBytes + 15) & ~size_t(15)) : a.inStride;
+  if (a.inUser)
+    for (int s = 0; s < n; ++s)
+      block_copy(const_cast<char*>(a.in[dc.rank]) + static_cast<size_t>(s) * workStride + off,
+                 a.inUser + static_cast<size_t>(s) * a.inStride + off, len);
+  if (!rank_barrier(dc)) return;
+  for (int p = 0; p < n; ++p) {
+    const int peer = (dc.rank + p) % n;
+    block_copy(a.outUser + static_cast<size_t>(peer) * a.outStride + off,
+               a.in[peer] + static_cast<size_t>(dc.rank) * workStride + off, len);
+  }
+  rank_barrier(dc);
+}
+
+// ------------------------------------------------------------------ kernel entry
+template <int K, int DT>
+__global__ void __launch_bounds__(kThreads, 1) coll_kernel(const __grid_constant__ CollArgs a) {
+  if (K == KERN_AR_ONESHOT) ar_oneshot<DT>(a);
+  if (K == KERN_AR_TWOSHOT) ar_twoshot<DT, false>(a);
+  if (K == KERN_AR_NVLS) ar_twoshot<DT, true>(a);
+  if (K == KERN_AR_LL) ar_ll<DT>(a);
+  if (K == KERN_AG_PULL) ag_pull(a);
+  if (K == KERN_AG_PUSH) ag_push(a);
+  if (K == KERN_RS_PULL) rs_pull<DT>(a);
+  if (K == KERN_BCAST_PULL) bcast_pull(a);
+  if (K == KERN_BCAST_PUSH) bcast_push(a);
+  if (K == KERN_REDUCE_PULL) reduce_pull<DT>(a);
+  if (K == KERN_A2A_PULL) a2a_pull(a);
+}
+
+}  // namespace dev
+
+template <int K>
+static cudaError_t launchTyped(const CollArgs& a, int blocks, cudaStream_t stream) {
+  switch (a.dtype) {
+    case dev::DT_F16: dev::coll_kernel<K, dev::DT_F16><<<blocks, dev::kThreads, 0, stream>>>(a); break;
+    case dev::DT_BF16: dev::coll_kernel<K, dev::DT_BF16><<<blocks, dev::kThreads, 0, stream>>>(a); break;
+    case dev::DT_F32: dev::coll_kernel<K, dev::DT_F32><<<blocks, dev::kThreads, 0, stream>>>(a); break;
+    default: return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+template <int K>
+static cudaError_t launchUntyped(const CollArgs& a, int blocks, cudaStream_t stream) {
+  dev::coll_kernel<K, dev::DT_F32><<<blocks, dev::kThreads, 0, stream>>>(a);
+  return cudaGetLastError();
+}
+
+cudaError_t launchCollKernel(CollKernel k, const CollArgs& a, int blocks, cudaStream_t stream) {
+  if (blocks < 1 || blocks > kMaxBlocks) return cudaErrorInvalidValue;
+  switch (k) {
+    case KERN_AR_ONESHOT: return launchTyped<KERN_AR_ONESHOT>(a, blocks, stream);
+    case KERN_AR_TWOSHOT: return launchTyped<KERN_AR_TWOSHOT>(a, blocks, stream);
+    case KERN_AR_NVLS: return launchTyped<KERN_AR_NVLS>(a, blocks, stream);
+    case KERN_AR_LL: return blocks <= kLLBlocks ? launchTyped<KERN_AR_LL>(a, blocks, stream) : cudaErrorInvalidValue;
+    case KERN_AG_PULL: return launchUntyped<KERN_AG_PULL>(a, blocks, stream);
+    case KERN_AG_PUSH: return launchUntyped<KERN_AG_PUSH>(a, blocks, stream);
+    case KERN_RS_PULL: return launchTyped<KERN_RS_PULL>(a, blocks, stream);
+    case KERN_BCAST_PULL: return launchUntyped<KERN_BCAST_PULL>(a, blocks, stream);
+    case KERN_BCAST_PUSH: return launchUntyped<KERN_BCAST_PUSH>(a, blocks, stream);
+    case KERN_REDUCE_PULL: return launchTyped<KERN_REDUCE_PULL>(a, blocks, stream);
+    case KERN_A2A_PULL: return launchUntyped<KERN_A2A_PULL>(a, blocks, stream);
+  }
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace uccl

@@ -1,0 +1,100 @@
+// Kernel argument blocks and launch entry points of the NVLink-domain collectives.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "device_comm.h"
+#include "uccl.h"
+
+namespace uccl {
+
+// One launch of a collective over the NVLink domain.  `in[p]` / `out[p]` are rank p's
+// peer-visible work buffers (the user's symmetric buffer, or the arena's staging area);
+// `inUser` / `outUser` are set when data must first be copied into / finally out of the local
+// work buffer because the user's buffer is not symmetric.
+struct CollArgs {
+  DevComm dc;
+  const char* inUser;
+  char* outUser;
+  const char* in[UCCL_MAX_LOCAL_RANKS];
+  char* out[UCCL_MAX_LOCAL_RANKS];
+  const char* inMc;   // multicast alias of `in` (NVLS) or nullptr
+  char* outMc;        // multicast alias of `out` or nullptr
+  size_t bytes;       // all-reduce / broadcast / reduce: work bytes of this launch, 16-byte padded
+  size_t userBytes;   // exact byte count behind `bytes` (or behind one chunk) in the user buffers
+  size_t chunkBytes;  // chunked collectives: bytes per rank chunk in the work buffers
+  size_t inStride;    // distance between consecutive rank chunks in inUser
+  size_t outStride;   // distance between consecutive rank chunks in outUser
+  int dtype;          // dev::DT_*
+  int root;
+  int vec;            // 1: every pointer/size is a 16-byte multiple
+};
+
+enum CollKernel : int {
+  KERN_AR_ONESHOT = 0,
+  KERN_AR_TWOSHOT = 1,
+  KERN_AR_NVLS = 2,
+  KERN_AR_LL = 3,
+  KERN_AG_PULL = 4,
+  KERN_AG_PUSH = 5,   // push with plain stores, or multimem.st when outMc is set
+  KERN_RS_PULL = 6,   // pull with plain loads, or multimem.ld_reduce when inMc is set
+  KERN_BCAST_PULL = 7,
+  KERN_BCAST_PUSH = 8,
+  KERN_REDUCE_PULL = 9,
+  KERN_A2A_PULL = 10,
+};
+
+cudaError_t launchCollKernel(CollKernel k, const CollArgs& a, int blocks, cudaStream_t stream);
+
+// Ring all-reduce / all-gather / reduce-scatter over peer-memory step FIFOs (Simple protocol)
+// and the LL128 line protocol; see ring.cu.
+struct RingArgs {
+  DevComm dc;
+  const char* inUser;
+  char* outUser;
+  size_t count;       // elements (all-reduce) or elements per rank chunk
+  int dtype;
+  int coll;           // ucclCollKind_t: AllReduce / AllGather / ReduceScatter
+  int proto;          // ucclProtoSimple / ucclProtoLL128
+  int ringPrev, ringNext;  // NVLink-domain indices of the ring neighbours
+  int ringPos;        // my position in the ring order
+  int ringRanks[UCCL_MAX_LOCAL_RANKS];  // ring order (position -> domain index)
+};
+cudaError_t launchRingKernel(const RingArgs& a, int blocks, cudaStream_t stream);
+
+// Point-to-point: each entry is one send or one receive through the receiver's arena slots.
+struct P2pOp {
+  int isSend;
+  int peer;       // NVLink-domain index
+  const char* src;
+  char* dst;
+  size_t bytes;
+};
+constexpr int kMaxP2pOps = 32;
+struct P2pArgs {
+  DevComm dc;
+  int nops;
+  P2pOp ops[kMaxP2pOps];
+};
+cudaError_t launchP2pKernel(const P2pArgs& a, cudaStream_t stream);
+
+// Fused all-reduce + residual add + RMSNorm, see fused_norm.cu.
+struct ArNormArgs {
+  DevComm dc;
+  const char* in[UCCL_MAX_LOCAL_RANKS];  // partial sums, symmetric or staged, [tokens, hidden] bf16
+  const char* inMc;
+  const char* inUser;                    // copy-in source when staged
+  const __nv_bfloat16* residual;         // [tokens, hidden] local
+  const __nv_bfloat16* gamma;            // [hidden]
+  char* out[UCCL_MAX_LOCAL_RANKS];       // normalised output, symmetric/staged
+  char* outMc;
+  char* outUser;                         // copy-out target when staged
+  char* resOut[UCCL_MAX_LOCAL_RANKS];    // updated residual, symmetric/staged (same rules)
+  char* resOutMc;
+  char* resOutUser;
+  int tokens, hidden;
+  float eps;
+};
+cudaError_t launchArNormKernel(const ArNormArgs& a, int blocks, cudaStream_t stream);
+
+}  // namespace uccl

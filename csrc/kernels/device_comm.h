@@ -1,0 +1,65 @@
+// Device-visible view of a communicator, passed by value to every collective kernel.
+// Plain C structs shared by host code and kernels.
+#pragma once
+#include <stddef.h>
+#include <stdint.h>
+
+#include "uccl.h"
+
+namespace uccl {
+
+constexpr int kMaxBlocks = 128;       // CTAs a collective kernel may use ("channels")
+constexpr int kLLBlocks = 16;         // CTAs the low-latency protocol may use
+constexpr int kLLDataPerBlock = 4096; // payload bytes per CTA per peer per LL operation
+constexpr int kLLSlotBytes = 2 * kLLDataPerBlock;  // each 8 data bytes travel with 8 flag bytes
+constexpr int kP2pSlots = 2;
+constexpr size_t kP2pSlotBytes = 2u << 20;
+
+// Arena layout (byte offsets inside every rank's symmetric arena).
+constexpr size_t kArenaBarrierOff = 0;                 // u32 [kMaxBlocks][UCCL_MAX_LOCAL_RANKS]
+constexpr size_t kArenaGemmReadyOff = 64u << 10;       // u32 [4096] all-gather arrival flags
+constexpr size_t kArenaGemmDoneOff = 80u << 10;        // u32 [4096] reduce-scatter counters
+constexpr size_t kArenaP2pCtrlOff = 96u << 10;         // P2pCtrl [UCCL_MAX_LOCAL_RANKS][kP2pStripes]
+constexpr size_t kArenaMoeCtrlOff = 128u << 10;        // MoE counters (see moe.cu)
+constexpr size_t kArenaLLOff = 1u << 20;               // [2][kLLBlocks][UCCL_MAX_LOCAL_RANKS][kLLSlotBytes]
+constexpr size_t kArenaLLBytes = 2ull * kLLBlocks * UCCL_MAX_LOCAL_RANKS * kLLSlotBytes;  // 4 MiB
+constexpr size_t kArenaP2pDataOff = kArenaLLOff + kArenaLLBytes;  // [nranks][kP2pSlots][kP2pSlotBytes]
+
+// Control words of the point-to-point FIFOs between this rank and one peer, for one stripe; the
+// arena holds P2pCtrl [UCCL_MAX_LOCAL_RANKS][kP2pStripes] indexed by peer.  All four counters
+// count slots since communicator creation.
+constexpr int kP2pStripes = 8;  // CTAs (and independent sub-FIFOs) per point-to-point operation
+struct P2pCtrl {
+  uint64_t tail;  // written remotely by the peer when it is the sender: slots it has filled for me
+  uint64_t head;  // written remotely by the peer when it is the receiver: slots of mine it has drained
+  uint64_t sent;  // local: slots I have filled for the peer
+  uint64_t rcvd;  // local: slots from the peer I have drained
+  uint64_t pad[4];
+};
+
+struct DevComm {
+  int rank;    // index inside the NVLink domain
+  int nranks;  // size of the NVLink domain
+  char* arena[UCCL_MAX_LOCAL_RANKS];  // every rank's arena, peer-mapped; arena[rank] is local
+  char* arenaMc;                      // multicast alias of the arena (NULL without NVLS)
+  uint32_t* epochs;                   // local device memory: u32 [kMaxBlocks] barrier epochs
+  uint32_t* llEpochs;                 // local device memory: u32 [kLLBlocks]
+  uint32_t* abortFlag;                // mapped host word; non-zero = give up
+  uint32_t* status;                   // mapped host u32 [8]: code, rank, peer, step, block
+  uint64_t timeoutNs;                 // budget of one device-side wait
+};
+
+// Error codes a kernel can leave in status[0].
+enum DevStatus : uint32_t {
+  DEV_OK = 0,
+  DEV_TIMEOUT_BARRIER = 1,
+  DEV_TIMEOUT_LL = 2,
+  DEV_TIMEOUT_P2P = 3,
+  DEV_TIMEOUT_NET = 4,
+  DEV_TIMEOUT_SIGNAL = 5,
+  DEV_TIMEOUT_GEMM = 6,
+  DEV_TIMEOUT_MOE = 7,
+  DEV_ABORTED = 100,
+};
+
+}  // namespace uccl

@@ -17,3 +17,7 @@ except ImportError as _e:  # pragma: no cover - exercised only on a broken check
     ) from _e
 
 __version__ = "0.1.0"
+
+from .communicator import Communicator, get_unique_id  # noqa: E402,F401
+
+__all__ = ["Communicator", "get_unique_id"]
