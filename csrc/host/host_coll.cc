@@ -133,12 +133,13 @@ ucclResult_t hostRunXfers(Comm* comm, std::vector<HostXfer>& xfers) {
       ucclResult_t err;
       // post as many sub-chunks as the FIFOs take
       while (x.posted < nsub) {
+        // a receive slot (and its FIFO entry) may only be re-posted after this thread consumed
+        // what it held: never keep more than UCCL_STEPS unconsumed receives per connection
+        if (!x.isSend && x.posted - x.done >= UCCL_STEPS * x.conns.size()) break;
         NetConn* c = x.conns[x.posted % x.conns.size()];
         if (connError(comm, c, &err)) return err;
         const uint64_t head = fifoLoadAcquire(&c->fifo->head);
         if (c->step - head >= UCCL_STEPS) break;  // no free slot on that connection yet
-        // a receive slot may only be re-posted after this thread consumed what it held;
-        // that is guaranteed because consumption below happens in posting order
         const size_t off = x.posted * slot;
         const size_t n = std::min(slot, x.len - off);
         uint64_t step = 0;
@@ -148,7 +149,6 @@ ucclResult_t hostRunXfers(Comm* comm, std::vector<HostXfer>& xfers) {
         x.steps.push_back(step);
         ++x.posted;
         moved = true;
-        if (!x.isSend && x.posted - x.done >= UCCL_STEPS * x.conns.size()) break;
       }
       // retire completed sub-chunks in order
       while (x.done < x.posted) {

@@ -1,0 +1,327 @@
+"""One rank of a multi-process test.  Usage: rank_worker.py <case> <rank> <nranks> <idfile> [args...]
+
+Prints a single line "RESULT <json>".  Cases are functions named case_<name> below; each gets
+(comm, rank, nranks, args) and returns a dict.  A non-empty "fail" list marks a failed check.
+"""
+import json
+import os
+import sys
+import time
+import traceback
+
+import torch
+
+
+def _uid(rank, idfile, create=True):
+    from unified_ccl_b200 import get_unique_id
+
+    if rank == 0 and create:
+        uid = get_unique_id()
+        with open(idfile + ".tmp", "wb") as f:
+            f.write(uid)
+        os.rename(idfile + ".tmp", idfile)
+        return uid
+    t0 = time.time()
+    while not os.path.exists(idfile):
+        if time.time() - t0 > 60:
+            raise RuntimeError("unique id file never appeared")
+        time.sleep(0.01)
+    with open(idfile, "rb") as f:
+        return f.read()
+
+
+def _seeded(count, seed, dtype=torch.float32):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.rand(count, generator=g) * 2 - 1).to(dtype)
+
+
+def _dev(comm, rank):
+    return torch.device("cuda", comm.info["cuda_device"]) if comm.on_gpu else torch.device("cpu")
+
+
+def _sync(comm):
+    if comm.on_gpu:
+        torch.cuda.synchronize()
+
+
+# ---------------------------------------------------------------------------- cases
+def case_allreduce_config1(comm, rank, n, args):
+    """fp32, 1,048,576 elements per rank, rank r seeded with 1234 + r, exact elementwise sum."""
+    count = 1048576
+    x = _seeded(count, 1234 + rank).to(_dev(comm, rank))
+    ref = sum(_seeded(count, 1234 + r) for r in range(n))
+    t0 = time.time()
+    comm.allreduce(x)
+    _sync(comm)
+    dt = time.time() - t0
+    err = (x.cpu() - ref).abs().max().item()
+    tol = 0.0 if n == 2 else 1e-5
+    return {"err": err, "seconds": dt, "fail": [] if err <= tol else [("allreduce", err)],
+            "proxy_posts": comm.counters()["proxy_posts"], "net": comm.info["net_name"]}
+
+
+def _collective_matrix(comm, rank, n, counts, dtypes, sym=False, inplace_ag=True):
+    dev = _dev(comm, rank)
+    fail = []
+
+    def mk(numel, dt):
+        return comm.empty(numel, dt) if sym else torch.empty(numel, dtype=dt, device=dev)
+
+    for dt in dtypes:
+        tol = {torch.float32: 1e-5, torch.bfloat16: 2e-2, torch.float16: 2e-3}[dt] * n
+        for cnt in counts:
+            # all-reduce, in place and out of place
+            xs = [_seeded(cnt, 1234 + r, dt) for r in range(n)]
+            ref = sum(x.float() for x in xs)
+            x = mk(cnt, dt)
+            x.copy_(xs[rank])
+            comm.allreduce(x)
+            _sync(comm)
+            e = (x.float().cpu() - ref).abs().max().item() if cnt else 0.0
+            if e > tol:
+                fail.append(("allreduce", str(dt), cnt, e))
+            src = xs[rank].to(dev)
+            out = mk(cnt, dt)
+            comm.allreduce(src, out=out)
+            _sync(comm)
+            e = (out.float().cpu() - ref).abs().max().item() if cnt else 0.0
+            if e > tol or not torch.equal(src.cpu(), xs[rank]):
+                fail.append(("allreduce_oop", str(dt), cnt, e))
+            # all-gather
+            s = torch.full((cnt,), float(rank + 1), dtype=dt, device=dev)
+            r = mk(cnt * n, dt)
+            comm.allgather(s, r)
+            _sync(comm)
+            exp = torch.cat([torch.full((cnt,), float(p + 1)) for p in range(n)]) if cnt else torch.empty(0)
+            if not torch.equal(r.float().cpu(), exp):
+                fail.append(("allgather", str(dt), cnt))
+            # reduce-scatter
+            full = [_seeded(cnt * n, 99 + p, dt) for p in range(n)]
+            s2 = mk(cnt * n, dt)
+            s2.copy_(full[rank])
+            r2 = torch.empty(cnt, dtype=dt, device=dev)
+            comm.reduce_scatter(s2, r2)
+            _sync(comm)
+            exp2 = sum(f.float() for f in full)[rank * cnt:(rank + 1) * cnt]
+            e = (r2.float().cpu() - exp2).abs().max().item() if cnt else 0.0
+            if e > tol:
+                fail.append(("reduce_scatter", str(dt), cnt, e))
+            # broadcast from the last rank
+            b = mk(cnt, dt)
+            b.fill_(float(rank))
+            comm.broadcast(b, root=n - 1)
+            _sync(comm)
+            if cnt and not (b.float().cpu() == n - 1).all():
+                fail.append(("broadcast", str(dt), cnt))
+            # reduce to rank 0
+            rd = mk(cnt, dt)
+            rd.copy_(xs[rank])
+            out2 = torch.zeros(cnt, dtype=dt, device=dev)
+            comm.reduce(rd, out2, root=0)
+            _sync(comm)
+            if rank == 0 and cnt:
+                e = (out2.float().cpu() - ref).abs().max().item()
+                if e > tol:
+                    fail.append(("reduce", str(dt), cnt, e))
+            # all-to-all
+            if cnt:
+                a = mk(cnt * n, dt)
+                a.copy_((torch.arange(n * cnt) % 251 + rank).to(dt))
+                a2 = torch.empty(cnt * n, dtype=dt, device=dev)
+                comm.alltoall(a, a2)
+                _sync(comm)
+                exp3 = torch.cat([(torch.arange(rank * cnt, (rank + 1) * cnt) % 251 + p).to(dt) for p in range(n)])
+                if not torch.equal(a2.cpu(), exp3):
+                    fail.append(("alltoall", str(dt), cnt))
+    return fail
+
+
+def case_collectives_small(comm, rank, n, args):
+    fail = _collective_matrix(comm, rank, n, [0, 1, 3, 257, 70001], [torch.float32, torch.bfloat16, torch.float16])
+    return {"fail": fail, "algo_hist": comm.counters()["algo_hist"]}
+
+
+def case_collectives_symmetric(comm, rank, n, args):
+    fail = _collective_matrix(comm, rank, n, [8, 4096, 70001, 1 << 20], [torch.bfloat16, torch.float32], sym=True)
+    return {"fail": fail, "nvls": comm.info["nvls"]}
+
+
+def case_allreduce_algos(comm, rank, n, args):
+    dev = _dev(comm, rank)
+    fail = []
+    combos = [("one_shot", "ll"), ("one_shot", "simple"), ("two_shot", "simple"), ("nvls", "simple"),
+              ("ring", "simple"), ("ring", "ll128"), ("copy_engine", "simple")]
+    for dt in (torch.bfloat16, torch.float32, torch.float16):
+        tol = {torch.float32: 1e-5, torch.bfloat16: 2e-2, torch.float16: 2e-3}[dt] * n
+        es = torch.empty((), dtype=dt).element_size()
+        for cnt in (1, 7, 1000, 4096, 65536 + 3, 1 << 20):
+            xs = [_seeded(cnt, 1234 + r, dt) for r in range(n)]
+            ref = sum(x.float() for x in xs)
+            for algo, proto in combos:
+                if proto == "ll" and cnt * es > 65536:
+                    continue
+                for sym in (False, True):
+                    comm.set_algo(algo, proto)
+                    x = comm.empty(cnt, dt) if sym else torch.empty(cnt, dtype=dt, device=dev)
+                    x.copy_(xs[rank])
+                    comm.allreduce(x)
+                    _sync(comm)
+                    e = (x.float().cpu() - ref).abs().max().item()
+                    if e > tol:
+                        fail.append((algo, proto, str(dt), cnt, sym, e))
+                    if sym:
+                        comm.free(x)
+    comm.set_algo("auto", "auto")
+    return {"fail": fail, "algo_hist": comm.counters()["algo_hist"], "nvls": comm.info["nvls"]}
+
+
+def case_sendrecv(comm, rank, n, args):
+    dev = _dev(comm, rank)
+    fail = []
+    for cnt in (5, 1 << 18, (5 << 20) + 77):
+        s = torch.full((cnt,), float(rank), device=dev)
+        r = torch.empty(cnt, device=dev)
+        with comm.group():
+            comm.send(s, (rank + 1) % n)
+            comm.recv(r, (rank - 1) % n)
+        _sync(comm)
+        if not (r.cpu() == (rank - 1) % n).all():
+            fail.append(("ring_exchange", cnt))
+    # ungrouped pair: even ranks send first, odd ranks receive first
+    if n % 2 == 0:
+        peer = rank ^ 1
+        s = torch.arange(1000, dtype=torch.float32, device=dev) + rank
+        r = torch.empty(1000, device=dev)
+        if rank % 2 == 0:
+            comm.send(s, peer)
+            comm.recv(r, peer)
+        else:
+            comm.recv(r, peer)
+            comm.send(s, peer)
+        _sync(comm)
+        if not torch.equal(r.cpu(), torch.arange(1000, dtype=torch.float32) + peer):
+            fail.append(("pair",))
+    # send to self inside a group
+    s = torch.full((64,), 7.0, device=dev)
+    r = torch.zeros(64, device=dev)
+    with comm.group():
+        comm.send(s, rank)
+        comm.recv(r, rank)
+    _sync(comm)
+    if not (r.cpu() == 7).all():
+        fail.append(("self",))
+    return {"fail": fail}
+
+
+def case_api_contract(comm, rank, n, args):
+    """The reference's Python test contract (tests/python/test_allreduce.py) on this backend."""
+    dev = _dev(comm, rank)
+    fail = []
+    for dt in (torch.float16, torch.bfloat16, torch.float32):
+        for size in (1, 16, 256, 1024, 4096, 65536):
+            t = torch.ones(size, dtype=dt, device=dev)
+            ptr = t.data_ptr()
+            out = comm.allreduce(t)
+            _sync(comm)
+            if out.data_ptr() != ptr:
+                fail.append(("not in place", str(dt), size))
+            if not torch.allclose(t.float().cpu(), torch.full((size,), float(n))):
+                fail.append(("value", str(dt), size))
+    try:
+        comm.allreduce(torch.ones(4, dtype=torch.int32, device=dev))
+        fail.append(("int32 accepted",))
+    except TypeError:
+        pass
+    try:
+        wrong = torch.ones(4, device="cpu" if comm.on_gpu else "meta")
+        comm.allreduce(wrong)
+        fail.append(("wrong device accepted",))
+    except (ValueError, NotImplementedError, RuntimeError):
+        pass
+    try:
+        comm.allgather(torch.ones(4, device=dev), torch.ones(5, device=dev))
+        fail.append(("bad allgather size accepted",))
+    except ValueError:
+        pass
+    if comm.rank != rank or comm.world_size != n:
+        fail.append(("rank/world_size",))
+    comm.destroy()
+    comm.destroy()  # idempotent
+    return {"fail": fail}
+
+
+def case_peer_exits(comm, rank, n, args):
+    """Rank n-1 leaves between steps; the others get an error on their next collective."""
+    dev = _dev(comm, rank)
+    x = torch.ones(1024, device=dev)
+    comm.allreduce(x)
+    _sync(comm)
+    ok_first = bool((x.cpu() == n).all())
+    if rank == n - 1:
+        return {"fail": [] if ok_first else [("first",)], "left": True, "_exit_now": True}
+    time.sleep(0.5)
+    t0 = time.time()
+    err = None
+    try:
+        y = torch.ones(1 << 20, device=dev)
+        comm.allreduce(y)
+        _sync(comm)
+        if comm.on_gpu:
+            comm.finalize()
+    except Exception as e:  # noqa: BLE001
+        err = str(e)
+    took = time.time() - t0
+    fail = []
+    if not ok_first:
+        fail.append(("first",))
+    if err is None and comm.async_error() == 0:
+        fail.append(("no error surfaced",))
+    return {"fail": fail, "err": err, "seconds": took, "async": comm.async_error(), "last": comm.last_error(),
+            "timeouts": comm.counters()["wait_timeouts"], "_abort": True}
+
+
+def main():
+    case, rank, n, idfile = sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), sys.argv[4]
+    args = sys.argv[5:]
+    res = {"rank": rank}
+    comm = None
+    try:
+        if torch.cuda.is_available() and os.environ.get("UCCL_BACKEND", "") != "cpu":
+            torch.cuda.set_device(rank % torch.cuda.device_count())
+        if case == "never_joins" and rank == n - 1:
+            _uid(rank, idfile)  # learn the id, then walk away without joining
+            print("RESULT " + json.dumps({"rank": rank, "absent": True}), flush=True)
+            return
+        from unified_ccl_b200 import Communicator
+
+        uid = _uid(rank, idfile)
+        if case == "never_joins":
+            t0 = time.time()
+            try:
+                Communicator(rank, n, unique_id=uid)
+                res["fail"] = [("init succeeded",)]
+            except Exception as e:  # noqa: BLE001
+                res["err"] = str(e)
+                res["seconds"] = time.time() - t0
+                res["fail"] = []
+            print("RESULT " + json.dumps(res), flush=True)
+            return
+        comm = Communicator(rank, n, unique_id=uid)
+        res.update(globals()["case_" + case](comm, rank, n, args))
+    except Exception:  # noqa: BLE001
+        res["exc"] = traceback.format_exc()
+    print("RESULT " + json.dumps(res, default=str), flush=True)
+    if res.get("_exit_now"):
+        os._exit(0)  # leave without tearing the communicator down, like a crashed rank
+    try:
+        if comm is not None:
+            if res.get("_abort"):
+                comm.abort()
+            else:
+                comm.destroy()
+    except Exception:  # noqa: BLE001
+        pass
+
+
+if __name__ == "__main__":
+    main()
