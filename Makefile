@@ -2,7 +2,10 @@
 # network plugin, all in-tree.  `make -j` is what __graft_entry__.build() runs.
 CUDA_HOME ?= /usr/local/cuda
 NVCC      ?= $(CUDA_HOME)/bin/nvcc
-CXX       ?= g++
+# Prefer the distribution compiler: it links libstdc++ dynamically, so the library shares the C++
+# runtime of the process that loads it (a toolchain with only a static libstdc++ also works, the
+# library code avoids iostreams for that case).
+CXX       := $(firstword $(wildcard /usr/bin/g++) g++)
 PYTHON    ?= python3
 
 PYINC     := $(shell $(PYTHON) -c "import sysconfig; print(sysconfig.get_paths()['include'])")
@@ -13,7 +16,7 @@ BUILD     := build
 PKG       := unified_ccl_b200
 INCLUDES  := -Iinclude -Icsrc -I$(CUDA_HOME)/include
 CXXFLAGS  := -O2 -g -std=c++17 -fPIC -Wall -Wno-unused-function -pthread $(INCLUDES)
-NVFLAGS   := -O3 -std=c++17 -lineinfo -gencode arch=compute_100a,code=sm_100a \
+NVFLAGS   := --extended-lambda -O3 -std=c++17 -lineinfo -gencode arch=compute_100a,code=sm_100a \
              -Xcompiler -fPIC,-Wall,-Wno-unused-function --expt-relaxed-constexpr $(INCLUDES)
 LDFLAGS   := -shared -L$(CUDA_HOME)/lib64 -lcudart_static -ldl -lpthread -lrt
 

@@ -47,6 +47,7 @@ const DriverApi& driverApi() {
     ok &= resolve("cuStreamWaitValue64", &api.streamWaitValue64);
     ok &= resolve("cuGetErrorString", &api.getErrorString);
     ok &= resolve("cuCtxGetCurrent", &api.ctxGetCurrent);
+    ok &= resolve("cuMemGetAddressRange", &api.memGetAddressRange);
     // Multicast objects are optional (absent on drivers/GPUs without NVLS).
     resolve("cuMulticastCreate", &api.multicastCreate);
     resolve("cuMulticastAddDevice", &api.multicastAddDevice);

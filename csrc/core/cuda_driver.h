@@ -32,6 +32,7 @@ struct DriverApi {
   decltype(&cuStreamWaitValue64) streamWaitValue64 = nullptr;
   decltype(&cuGetErrorString) getErrorString = nullptr;
   decltype(&cuCtxGetCurrent) ctxGetCurrent = nullptr;
+  decltype(&cuMemGetAddressRange) memGetAddressRange = nullptr;
 };
 
 // Returns the process-wide table; `ok` is false when no driver is present.

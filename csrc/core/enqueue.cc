@@ -120,8 +120,11 @@ ucclResult_t arDirect(Comm* c, const CollOp& op, size_t bytes, const TuneChoice&
   const CollKernel kern = algo == ucclAlgoOneShot ? KERN_AR_ONESHOT : (algo == ucclAlgoNvls ? KERN_AR_NVLS : KERN_AR_TWOSHOT);
 
   if (algo == ucclAlgoOneShot) {
-    // inputs must be peer-visible; the output is written locally only
-    const size_t cap = sIn ? bytes : ((st.bytes / 2) & ~size_t(15));
+    // inputs must be peer-visible; the output is written locally only.  In place on a symmetric
+    // buffer the output would overwrite what peers are still reading, so it takes a detour
+    // through the staging area and is copied out after the closing barrier.
+    const bool inPlaceSym = sIn && send == recv;
+    const size_t cap = (sIn && !inPlaceSym) ? bytes : ((st.bytes / 2) & ~size_t(15));
     for (size_t po = 0; po < bytes; po += cap) {
       const size_t ub = std::min(cap, bytes - po), wb = up16(ub);
       CollArgs a;
@@ -134,7 +137,7 @@ ucclResult_t arDirect(Comm* c, const CollOp& op, size_t bytes, const TuneChoice&
         for (int p = 0; p < n; ++p) a.in[p] = st.peer[p];
         a.inUser = send + po;
       }
-      if ((ub & 15) == 0) {
+      if ((ub & 15) == 0 && !inPlaceSym) {
         a.out[c->localRank] = recv + po;
       } else {
         a.out[c->localRank] = st.peer[c->localRank] + st.bytes / 2;

@@ -39,6 +39,8 @@ size_t stagingOffset(const Comm* c);
 // device-side algorithms that live in their own translation units
 ucclResult_t enqueueRing(Comm* c, const CollOp& op, ucclProto_t proto, int blocks);
 ucclResult_t enqueueCopyEngine(Comm* c, const CollOp& op);
+// A stream-ordered barrier among the ranks of the NVLink domain (one tiny kernel).
+ucclResult_t enqueueBarrier(Comm* c, cudaStream_t s);
 ucclResult_t enqueueNetGpu(Comm* c, const CollOp& op);
 ucclResult_t enqueueNetGpuP2p(Comm* c, const std::vector<CollOp>& ops);
 

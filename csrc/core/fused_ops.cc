@@ -1,0 +1,252 @@
+// Fused compute + collective entry points: all-reduce + residual + RMSNorm, all-gather -> GEMM,
+// GEMM -> reduce-scatter.  None of them exists in the reference; they are the tensor-parallel
+// building blocks the library is benchmarked on (a Llama-style MLP block: sequence-parallel
+// activations are gathered in front of the column-parallel up/gate projection and the
+// row-parallel down projection ends in a reduce-scatter).
+#include <string.h>
+
+#include <algorithm>
+
+#include "../kernels/collectives.cuh"
+#include "../kernels/gemm_sm100.h"
+#include "enqueue.h"
+#include "log.h"
+
+using namespace uccl;
+
+namespace {
+
+struct DeviceGuard {
+  int prev = -1, want;
+  explicit DeviceGuard(int dev) : want(dev) {
+    cudaGetDevice(&prev);
+    if (prev != want) cudaSetDevice(want);
+  }
+  ~DeviceGuard() {
+    if (prev >= 0 && prev != want) cudaSetDevice(prev);
+  }
+};
+
+ucclResult_t validate(Comm* c) {
+  if (!commValid(c)) return ucclInvalidArgument;
+  if (c->abortFlag.load()) return ucclInvalidUsage;
+  const int ae = c->asyncError.load();
+  if (ae != ucclSuccess) return static_cast<ucclResult_t>(ae);
+  if (c->backend != BACKEND_CUDA) {
+    commSetError(c, "fused kernels need a communicator on GPUs");
+    return ucclInvalidUsage;
+  }
+  if (c->nRanks > 1 && (!c->p2pReady || c->useNet)) {
+    commSetError(c, "fused kernels need all ranks in one NVLink domain");
+    return ucclInvalidUsage;
+  }
+  return ucclSuccess;
+}
+
+struct Sym {
+  SymSegment* seg = nullptr;
+  size_t off = 0;
+};
+bool symOf(Comm* c, const void* p, size_t bytes, Sym* out) {
+  if (!c->p2pReady || (reinterpret_cast<uintptr_t>(p) & 15)) return false;
+  SymSegment* s = c->heap.find(p, bytes);
+  if (!s) return false;
+  out->seg = s;
+  out->off = static_cast<size_t>(static_cast<const char*>(p) - s->local);
+  return true;
+}
+
+}  // namespace
+
+extern "C" ucclResult_t ucclAllReduceResidualRMSNorm(const void* x, const void* residual, const void* gamma, void* out,
+                                                     void* residualOut, int tokens, int hidden, float eps,
+                                                     ucclComm_t comm, void* stream) {
+  Comm* c = toComm(comm);
+  ucclResult_t r = validate(c);
+  if (r != ucclSuccess) return r;
+  if (!x || !residual || !gamma || !out || !residualOut || tokens <= 0 || hidden <= 0) return ucclInvalidArgument;
+  if (hidden % 8 != 0 || hidden > 16384) {
+    commSetError(c, "hidden must be a multiple of 8 and at most 16384");
+    return ucclInvalidArgument;
+  }
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(gamma) |
+       reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(residualOut)) & 15)
+    return ucclInvalidArgument;
+  DeviceGuard guard(c->cudaDev);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const size_t bytes = static_cast<size_t>(tokens) * hidden * 2;
+  const int n = c->localRanks;
+  ArNormArgs a;
+  memset(&a, 0, sizeof(a));
+  a.dc = c->dev;
+  a.residual = static_cast<const __nv_bfloat16*>(residual);
+  a.gamma = static_cast<const __nv_bfloat16*>(gamma);
+  a.outLocal = static_cast<char*>(out);
+  a.tokens = tokens;
+  a.hidden = hidden;
+  a.eps = eps;
+  commCount(c, ucclCollAllReduce, bytes, c->arena && c->arena->mc ? ucclAlgoNvls : ucclAlgoTwoShot);
+  if (c->nRanks == 1) {
+    a.dc.nranks = 1;
+    a.inUser = static_cast<const char*>(x);
+    a.resOutUser = static_cast<char*>(residualOut);
+    const int blocks = std::min(kMaxBlocks, std::max(1, tokens));
+    if (launchArNormKernel(a, blocks, s) != cudaSuccess) {
+      commSetError(c, "norm kernel launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+      return ucclSystemError;
+    }
+    return ucclSuccess;
+  }
+  const size_t stageOff = stagingOffset(c);
+  const size_t half = ((c->cfg.stagingBytes & ~size_t(4095)) / 2) & ~size_t(255);
+  Sym sx, sr;
+  const bool symX = symOf(c, x, bytes, &sx);
+  const bool symR = symOf(c, residualOut, bytes, &sr);
+  if ((!symX || !symR) && bytes > half) {
+    commSetError(c, "tensor of %zu bytes does not fit the staging area; allocate x and residual_out with ucclMemAlloc "
+                    "or raise UCCL_STAGING_BYTES", bytes);
+    return ucclInvalidUsage;
+  }
+  for (int p = 0; p < n; ++p) {
+    a.in[p] = symX ? sx.seg->peer[p] + sx.off : c->arena->peer[p] + stageOff;
+    a.resOut[p] = symR ? sr.seg->peer[p] + sr.off : c->arena->peer[p] + stageOff + half;
+  }
+  if (symX) a.inMc = sx.seg->mc ? sx.seg->mc + sx.off : nullptr;
+  else {
+    a.inMc = c->arena->mc ? c->arena->mc + stageOff : nullptr;
+    a.inUser = static_cast<const char*>(x);
+  }
+  if (symR) a.resOutMc = sr.seg->mc ? sr.seg->mc + sr.off : nullptr;
+  else {
+    a.resOutMc = c->arena->mc ? c->arena->mc + stageOff + half : nullptr;
+    a.resOutUser = static_cast<char*>(residualOut);
+  }
+  if (c->forcedAlgo == ucclAlgoTwoShot || c->forcedAlgo == ucclAlgoOneShot) a.inMc = nullptr, a.resOutMc = nullptr;
+  int blocks = c->cfg.maxCtas > 0 ? std::min(c->cfg.maxCtas, kMaxBlocks) : 64;
+  blocks = std::min(blocks, std::max(1, (tokens + n - 1) / n));
+  if (launchArNormKernel(a, blocks, s) != cudaSuccess) {
+    commSetError(c, "fused norm kernel launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+    return ucclSystemError;
+  }
+  return ucclSuccess;
+}
+
+extern "C" ucclResult_t ucclAllGatherGemm(const void* xShard, void* xFull, const void* W, void* C, int M, int N, int K,
+                                          int epilogue, ucclComm_t comm, void* stream) {
+  Comm* c = toComm(comm);
+  ucclResult_t r = validate(c);
+  if (r != ucclSuccess) return r;
+  if (!xShard || !xFull || !W || !C || M <= 0 || N <= 0 || K <= 0 || (epilogue != 0 && epilogue != 1))
+    return ucclInvalidArgument;
+  DeviceGuard guard(c->cudaDev);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int n = c->localRanks;
+  GemmLaunch g;
+  g.A = xFull;
+  g.B = W;
+  g.C = C;
+  g.M = M;
+  g.N = N;
+  g.K = K;
+  g.lda = K;
+  g.ldb = K;
+  g.ldc = epilogue == 1 ? N / 2 : N;
+  g.epilogue = epilogue;
+  g.err = c->hostFlagsDev + 16;
+  if (c->nRanks == 1) {
+    g.A = xShard;
+    return launchGemmBf16(g, nullptr, s);
+  }
+  if (M % n != 0 || (M / n) % 128 != 0) {
+    commSetError(c, "all-gather GEMM needs M / nranks to be a multiple of 128 (M=%d, nranks=%d)", M, n);
+    return ucclInvalidArgument;
+  }
+  if (M / 128 > 4096) return ucclInvalidArgument;
+  Sym sf;
+  if (!symOf(c, xFull, static_cast<size_t>(M) * K * 2, &sf)) {
+    commSetError(c, "xFull must come from ucclMemAlloc");
+    return ucclInvalidArgument;
+  }
+  // arrival flags start at zero; nobody pushes before every rank has cleared its own
+  uint32_t* ready = reinterpret_cast<uint32_t*>(c->arena->local + kArenaGemmReadyOff);
+  if (cudaMemsetAsync(ready, 0, sizeof(uint32_t) * (M / 128), s) != cudaSuccess) return ucclSystemError;
+  if ((r = enqueueBarrier(c, s)) != ucclSuccess) return r;
+  GemmFusion f;
+  f.role = 1;
+  f.rank = c->localRank;
+  f.nranks = n;
+  f.comm_ctas = c->cfg.maxCtas > 0 ? std::min(c->cfg.maxCtas, 32) : 16;
+  f.epoch = 1;
+  f.timeout_ns = c->dev.timeoutNs;
+  f.abort_flag = c->dev.abortFlag;
+  f.rows_per_rank = M / n;
+  f.a_local = xShard;
+  f.use_multimem = (sf.seg->mc && c->forcedAlgo != ucclAlgoTwoShot) ? 1 : 0;
+  f.a_full_mc = sf.seg->mc ? sf.seg->mc + sf.off : nullptr;
+  for (int p = 0; p < n; ++p) {
+    f.a_full_peer[p] = sf.seg->peer[p] + sf.off;
+    f.ready_peer[p] = reinterpret_cast<uint32_t*>(c->arena->peer[p] + kArenaGemmReadyOff);
+  }
+  commCount(c, ucclCollAllGather, static_cast<size_t>(M) * K * 2, f.use_multimem ? ucclAlgoNvls : ucclAlgoTwoShot);
+  return launchGemmBf16(g, &f, s);
+}
+
+extern "C" ucclResult_t ucclGemmReduceScatter(const void* A, const void* W, void* cPartial, void* out, int M, int N,
+                                              int K, ucclComm_t comm, void* stream) {
+  Comm* c = toComm(comm);
+  ucclResult_t r = validate(c);
+  if (r != ucclSuccess) return r;
+  if (!A || !W || !cPartial || !out || M <= 0 || N <= 0 || K <= 0) return ucclInvalidArgument;
+  DeviceGuard guard(c->cudaDev);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int n = c->localRanks;
+  GemmLaunch g;
+  g.A = A;
+  g.B = W;
+  g.C = cPartial;
+  g.M = M;
+  g.N = N;
+  g.K = K;
+  g.lda = K;
+  g.ldb = K;
+  g.ldc = N;
+  g.err = c->hostFlagsDev + 16;
+  if (c->nRanks == 1) {
+    g.C = out;
+    return launchGemmBf16(g, nullptr, s);
+  }
+  if (M % n != 0 || (M / n) % 128 != 0 || N % 8 != 0) {
+    commSetError(c, "GEMM reduce-scatter needs M / nranks to be a multiple of 128 and N a multiple of 8");
+    return ucclInvalidArgument;
+  }
+  if (M / 128 > 4096) return ucclInvalidArgument;
+  Sym sp;
+  if (!symOf(c, cPartial, static_cast<size_t>(M) * N * 2, &sp)) {
+    commSetError(c, "cPartial must come from ucclMemAlloc");
+    return ucclInvalidArgument;
+  }
+  uint32_t* done = reinterpret_cast<uint32_t*>(c->arena->local + kArenaGemmDoneOff);
+  if (cudaMemsetAsync(done, 0, sizeof(uint32_t) * (M / 128), s) != cudaSuccess) return ucclSystemError;
+  if ((r = enqueueBarrier(c, s)) != ucclSuccess) return r;
+  GemmFusion f;
+  f.role = 2;
+  f.rank = c->localRank;
+  f.nranks = n;
+  f.comm_ctas = c->cfg.maxCtas > 0 ? std::min(c->cfg.maxCtas, 32) : 16;
+  f.epoch = 1;
+  f.timeout_ns = c->dev.timeoutNs;
+  f.abort_flag = c->dev.abortFlag;
+  f.rows_per_rank = M / n;
+  f.use_multimem = (sp.seg->mc && c->forcedAlgo != ucclAlgoTwoShot) ? 1 : 0;
+  f.c_part_mc = sp.seg->mc ? sp.seg->mc + sp.off : nullptr;
+  for (int p = 0; p < n; ++p) {
+    f.c_part_peer[p] = sp.seg->peer[p] + sp.off;
+    f.done_peer[p] = reinterpret_cast<uint32_t*>(c->arena->peer[p] + kArenaGemmDoneOff);
+  }
+  f.rs_out = out;
+  f.rs_ldo = N;
+  commCount(c, ucclCollReduceScatter, static_cast<size_t>(M) * N * 2, f.use_multimem ? ucclAlgoNvls : ucclAlgoTwoShot);
+  if ((r = launchGemmBf16(g, &f, s)) != ucclSuccess) return r;
+  // peers may still be reading this rank's partial tiles: nobody reuses cPartial before all are done
+  return enqueueBarrier(c, s);
+}

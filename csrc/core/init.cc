@@ -202,7 +202,9 @@ ucclResult_t initRank(Comm* c, const ucclUniqueId& id) {
     cudaFree(0);  // make sure the primary context exists before any driver call
   }
 
+  UCCL_LOG(TRACE, "init: backend %s dev %d, starting bootstrap", c->backend == BACKEND_CUDA ? "cuda" : "cpu", c->cudaDev);
   r = c->bootstrap.init(id, c->rank, c->nRanks, c->cfg, &c->abortFlag);
+  UCCL_LOG(TRACE, "init: bootstrap done (%d)", (int)r);
   if (r != ucclSuccess) {
     commSetError(c, "bootstrap failed: %s", c->bootstrap.lastError().c_str());
     return r;
@@ -253,6 +255,7 @@ ucclResult_t initRank(Comm* c, const ucclUniqueId& id) {
   c->localRank = c->peers[c->rank].localRank;
   c->localRanks = static_cast<int>(c->localGlobalRanks.size());
 
+  UCCL_LOG(TRACE, "init: peers exchanged, nodes=%d localRanks=%d", c->nNodes, c->localRanks);
   // topology + tuner priors
   bool p2pCapable = false;
   if (c->backend == BACKEND_CUDA) {
@@ -281,8 +284,10 @@ ucclResult_t initRank(Comm* c, const ucclUniqueId& id) {
   const bool multiNode = c->nNodes > 1;
   c->useNet = c->nRanks > 1 && (multiNode || c->cfg.forceNet || c->backend == BACKEND_CPU || !p2pCapable);
 
+  UCCL_LOG(TRACE, "init: p2pCapable=%d useNet=%d", (int)p2pCapable, (int)c->useNet);
   if (c->backend == BACKEND_CUDA) {
     if ((r = setupCuda(c)) != ucclSuccess) return r;
+    UCCL_LOG(TRACE, "init: device state ready");
     if (!multiNode && p2pCapable && c->nRanks >= 1) {
       if ((r = setupArena(c)) != ucclSuccess) {
         if (c->nRanks == 1) return r;

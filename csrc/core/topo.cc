@@ -6,9 +6,7 @@
 #include <string.h>
 
 #include <algorithm>
-#include <fstream>
 #include <map>
-#include <sstream>
 
 #include "cuda_driver.h"
 #include "log.h"
@@ -41,23 +39,39 @@ static std::string lower(std::string s) {
   return s;
 }
 
+// The sysfs readers use stdio on purpose: this shared object carries its own copy of the C++
+// runtime, whose stream locale machinery is not set up when the object is loaded into a host
+// process, so formatted iostream extraction is off limits in library code.
+static bool readFirstLine(const std::string& path, char* buf, size_t len) {
+  FILE* f = fopen(path.c_str(), "r");
+  if (!f) return false;
+  const bool ok = fgets(buf, static_cast<int>(len), f) != nullptr;
+  fclose(f);
+  return ok;
+}
+
 int readNumaNode(const std::string& busId, const std::string& sysfsRoot) {
-  std::ifstream f(sysfsRoot + "/bus/pci/devices/" + lower(busId) + "/numa_node");
-  int v = -1;
-  if (f && (f >> v)) return v;
-  return -1;
+  char buf[64];
+  if (!readFirstLine(sysfsRoot + "/bus/pci/devices/" + lower(busId) + "/numa_node", buf, sizeof(buf))) return -1;
+  char* end = nullptr;
+  const long v = strtol(buf, &end, 10);
+  return end == buf ? -1 : static_cast<int>(v);
 }
 
 int numaToSocket(int numaNode, const std::string& sysfsRoot) {
   if (numaNode < 0) return -1;
-  std::ifstream f(sysfsRoot + "/devices/system/node/node" + std::to_string(numaNode) + "/cpulist");
-  std::string list;
-  if (!f || !std::getline(f, list) || list.empty()) return -1;
-  int cpu = atoi(list.c_str());  // first CPU of the list ("0-31,64-95" -> 0)
-  std::ifstream p(sysfsRoot + "/devices/system/cpu/cpu" + std::to_string(cpu) + "/topology/physical_package_id");
-  int pkg = -1;
-  if (p && (p >> pkg)) return pkg;
-  return -1;
+  char buf[256];
+  char name[64];
+  snprintf(name, sizeof(name), "%d", numaNode);
+  if (!readFirstLine(sysfsRoot + "/devices/system/node/node" + name + "/cpulist", buf, sizeof(buf))) return -1;
+  char* end = nullptr;
+  const long cpu = strtol(buf, &end, 10);  // first CPU of the list ("0-31,64-95" -> 0)
+  if (end == buf) return -1;
+  snprintf(name, sizeof(name), "%ld", cpu);
+  if (!readFirstLine(sysfsRoot + "/devices/system/cpu/cpu" + name + "/topology/physical_package_id", buf, sizeof(buf)))
+    return -1;
+  const long pkg = strtol(buf, &end, 10);
+  return end == buf ? -1 : static_cast<int>(pkg);
 }
 
 TopoLink classifyLink(const TopoGpu& a, const TopoGpu& b, const P2pFacts& f, bool nvswitch) {
@@ -125,17 +139,24 @@ ucclResult_t topoDetect(TopoSystem* sys, const std::vector<int>& devs) {
     g.dev = devs[i];
     g.rank = static_cast<int>(i);
     if (g.dev < 0 || g.dev >= visible) continue;
+    UCCL_LOG(TRACE, "topo: querying device %d", g.dev);
     char bus[32] = {0};
     if (cudaDeviceGetPCIBusId(bus, sizeof(bus), g.dev) == cudaSuccess) {
+      UCCL_LOG(TRACE, "topo: bus id %s", bus);
       g.busId = bus;
       g.busIdNum = parseBusId(g.busId);
+      UCCL_LOG(TRACE, "topo: bus num %lld", (long long)g.busIdNum);
       g.numaNode = readNumaNode(g.busId);
+      UCCL_LOG(TRACE, "topo: numa %d", g.numaNode);
       g.socket = numaToSocket(g.numaNode);
     } else {
       (void)cudaGetLastError();
     }
+    UCCL_LOG(TRACE, "topo: device %d bus %s numa %d socket %d", g.dev, g.busId.c_str(), g.numaNode, g.socket);
     cudaDeviceGetAttribute(&g.smCount, cudaDevAttrMultiProcessorCount, g.dev);
+    UCCL_LOG(TRACE, "topo: device %d sms %d", g.dev, g.smCount);
     const DriverApi& d = driverApi();
+    UCCL_LOG(TRACE, "topo: driver api ok=%d", (int)d.ok);
     if (d.ok) {
       CUdevice cd;
       int v = 0;
@@ -157,6 +178,7 @@ ucclResult_t topoDetect(TopoSystem* sys, const std::vector<int>& devs) {
         f.nativeAtomics = 1;
         continue;
       }
+      UCCL_LOG(TRACE, "topo: p2p attributes %d -> %d", a, b);
       cudaDeviceGetP2PAttribute(&f.access, cudaDevP2PAttrAccessSupported, a, b);
       cudaDeviceGetP2PAttribute(&f.nativeAtomics, cudaDevP2PAttrNativeAtomicSupported, a, b);
       cudaDeviceGetP2PAttribute(&f.perfRank, cudaDevP2PAttrPerformanceRank, a, b);

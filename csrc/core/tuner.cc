@@ -7,9 +7,7 @@
 #include <strings.h>
 
 #include <algorithm>
-#include <fstream>
 #include <map>
-#include <sstream>
 
 #include "../kernels/device_comm.h"
 #include "config.h"
@@ -182,14 +180,17 @@ bool Tuner::loadText(const std::string& json, std::string* why) {
 }
 
 bool Tuner::loadFile(const std::string& path, std::string* why) {
-  std::ifstream f(path);
+  FILE* f = fopen(path.c_str(), "rb");
   if (!f) {
     if (why) *why = "cannot open " + path;
     return false;
   }
-  std::stringstream ss;
-  ss << f.rdbuf();
-  return loadText(ss.str(), why);
+  std::string text;
+  char buf[4096];
+  size_t n;
+  while ((n = fread(buf, 1, sizeof(buf), f)) > 0) text.append(buf, n);
+  fclose(f);
+  return loadText(text, why);
 }
 
 void Tuner::addPoint(ucclCollKind_t coll, ucclAlgo_t algo, ucclProto_t proto, size_t bytes, float us, int blocks) {

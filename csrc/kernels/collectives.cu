@@ -380,6 +380,31 @@ __device__ void a2a_pull(const CollArgs& a) {
   rank_barrier(dc);
 }
 
+// ------------------------------------------------------------------ helpers of copy-engine mode
+template <int DT>
+__device__ void local_reduce(const CollArgs& a) {
+  using V = Vec<DT>;
+  const int B = gridDim.x, b = blockIdx.x, nslots = a.root;
+  size_t off, len;
+  slice16(a.bytes, B, b, &off, &len);
+  const char* src = a.in[0];
+  char* dst = a.out[0];
+  const size_t stride = static_cast<size_t>(blockDim.x) << 4;
+  for (size_t i = off + (static_cast<size_t>(threadIdx.x) << 4); i < off + len; i += stride) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int s = 0; s < nslots; ++s) V::add(acc, ptx::ld_global_v4(src + static_cast<size_t>(s) * a.inStride + i));
+    const uint4 v = V::pack(acc);
+    if (i + 16 <= a.userBytes) {
+      st_out16(dst + i, v);
+    } else {
+      // last, partial vector: element stores only
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+      for (size_t k = 0; i + k < a.userBytes; k += 2)
+        *reinterpret_cast<uint16_t*>(dst + i + k) = static_cast<uint16_t>(w[k >> 2] >> (8 * (k & 3)));
+    }
+  }
+}
+
 // ------------------------------------------------------------------ kernel entry
 template <int K, int DT>
 __global__ void __launch_bounds__(kThreads, 1) coll_kernel(const __grid_constant__ CollArgs a) {
@@ -394,6 +419,8 @@ __global__ void __launch_bounds__(kThreads, 1) coll_kernel(const __grid_constant
   if (K == KERN_BCAST_PUSH) bcast_push(a);
   if (K == KERN_REDUCE_PULL) reduce_pull<DT>(a);
   if (K == KERN_A2A_PULL) a2a_pull(a);
+  if (K == KERN_BARRIER) rank_barrier(a.dc);
+  if (K == KERN_LOCAL_REDUCE) local_reduce<DT>(a);
 }
 
 }  // namespace dev
@@ -428,6 +455,8 @@ cudaError_t launchCollKernel(CollKernel k, const CollArgs& a, int blocks, cudaSt
     case KERN_BCAST_PUSH: return launchUntyped<KERN_BCAST_PUSH>(a, blocks, stream);
     case KERN_REDUCE_PULL: return launchTyped<KERN_REDUCE_PULL>(a, blocks, stream);
     case KERN_A2A_PULL: return launchUntyped<KERN_A2A_PULL>(a, blocks, stream);
+    case KERN_BARRIER: return launchUntyped<KERN_BARRIER>(a, 1, stream);
+    case KERN_LOCAL_REDUCE: return launchTyped<KERN_LOCAL_REDUCE>(a, blocks, stream);
   }
   return cudaErrorInvalidValue;
 }

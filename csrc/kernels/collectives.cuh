@@ -42,6 +42,8 @@ enum CollKernel : int {
   KERN_BCAST_PUSH = 8,
   KERN_REDUCE_PULL = 9,
   KERN_A2A_PULL = 10,
+  KERN_BARRIER = 11,       // a rank barrier and nothing else (copy-engine mode)
+  KERN_LOCAL_REDUCE = 12,  // out[0] = sum of `root` local slots of in[0], inStride apart
 };
 
 cudaError_t launchCollKernel(CollKernel k, const CollArgs& a, int blocks, cudaStream_t stream);
@@ -59,6 +61,8 @@ struct RingArgs {
   int ringPrev, ringNext;  // NVLink-domain indices of the ring neighbours
   int ringPos;        // my position in the ring order
   int ringRanks[UCCL_MAX_LOCAL_RANKS];  // ring order (position -> domain index)
+  size_t ringBufOff;  // Simple protocol: offset of the step buffers inside the arena
+  size_t ringBufBytes;  // and their total size (split evenly over the channels)
 };
 cudaError_t launchRingKernel(const RingArgs& a, int blocks, cudaStream_t stream);
 
@@ -81,17 +85,15 @@ cudaError_t launchP2pKernel(const P2pArgs& a, cudaStream_t stream);
 // Fused all-reduce + residual add + RMSNorm, see fused_norm.cu.
 struct ArNormArgs {
   DevComm dc;
-  const char* in[UCCL_MAX_LOCAL_RANKS];  // partial sums, symmetric or staged, [tokens, hidden] bf16
-  const char* inMc;
-  const char* inUser;                    // copy-in source when staged
-  const __nv_bfloat16* residual;         // [tokens, hidden] local
+  const char* in[UCCL_MAX_LOCAL_RANKS];  // every rank's partial sums [tokens, hidden] bf16, peer-visible
+  const char* inMc;                      // multicast alias of `in` or nullptr
+  const char* inUser;                    // set when `in` is the staging area: copy from here first
+  const __nv_bfloat16* residual;         // [tokens, hidden], local
   const __nv_bfloat16* gamma;            // [hidden]
-  char* out[UCCL_MAX_LOCAL_RANKS];       // normalised output, symmetric/staged
-  char* outMc;
-  char* outUser;                         // copy-out target when staged
-  char* resOut[UCCL_MAX_LOCAL_RANKS];    // updated residual, symmetric/staged (same rules)
+  char* outLocal;                        // normalised output [tokens, hidden], local
+  char* resOut[UCCL_MAX_LOCAL_RANKS];    // every rank's new residual stream, peer-visible
   char* resOutMc;
-  char* resOutUser;
+  char* resOutUser;                      // set when `resOut` is the staging area: copy there last
   int tokens, hidden;
   float eps;
 };

@@ -23,7 +23,26 @@ constexpr size_t kArenaP2pCtrlOff = 96u << 10;         // P2pCtrl [UCCL_MAX_LOCA
 constexpr size_t kArenaMoeCtrlOff = 128u << 10;        // MoE counters (see moe.cu)
 constexpr size_t kArenaLLOff = 1u << 20;               // [2][kLLBlocks][UCCL_MAX_LOCAL_RANKS][kLLSlotBytes]
 constexpr size_t kArenaLLBytes = 2ull * kLLBlocks * UCCL_MAX_LOCAL_RANKS * kLLSlotBytes;  // 4 MiB
-constexpr size_t kArenaP2pDataOff = kArenaLLOff + kArenaLLBytes;  // [nranks][kP2pSlots][kP2pSlotBytes]
+// LL128 ring: per channel kRingSlots slots of kRingLLLines 128-byte lines, written by the ring
+// predecessor.  The region is only ever written with LL128 lines, so a stale word can never be
+// mistaken for a current flag.
+constexpr int kRingSlots = 4;
+constexpr int kRingLLLines = 64;                          // 64 lines = 8 KiB = 7168 payload bytes
+constexpr size_t kArenaRingLLOff = kArenaLLOff + kArenaLLBytes;
+constexpr size_t kArenaRingLLBytes = 1u << 20;            // [kLLBlocks][kRingSlots][kRingLLLines][128]
+constexpr size_t kArenaP2pDataOff = kArenaRingLLOff + kArenaRingLLBytes;  // [nranks][kP2pSlots][kP2pSlotBytes]
+constexpr size_t kArenaRingCtrlOff = 176u << 10;          // RingCtrl [kMaxBlocks]
+
+// Flow control of one ring channel (CTA).  `tail` is written by the ring predecessor (slots it
+// filled for me), `head` by the successor (slots of mine it drained); `sent` / `rcvd` are this
+// rank's own running counts.  All count slots since communicator creation.
+struct RingCtrl {
+  uint64_t tail;
+  uint64_t head;
+  uint64_t sent;
+  uint64_t rcvd;
+  uint64_t pad[4];
+};
 
 // Control words of the point-to-point FIFOs between this rank and one peer, for one stripe; the
 // arena holds P2pCtrl [UCCL_MAX_LOCAL_RANKS][kP2pStripes] indexed by peer.  All four counters

@@ -124,9 +124,10 @@ ucclResult_t launchGemmBf16(const GemmLaunch& g, const GemmFusion* f, cudaStream
     if (role == gemm::kCommAllGatherPush) {
       a.a_ready = f->ready_peer[f->rank];
       a.a_ready_target = f->epoch;
-      a.a_local_lo = f->rank * blk_per_rank;
-      a.a_local_hi = a.a_local_lo + blk_per_rank;
-      a.m_rot = a.a_local_lo;  // start with the rows that are already here
+      // the local shard is copied into A_full by the communication CTAs as well, so its rows
+      // are awaited like everybody else's; they simply arrive first, hence the rotation
+      a.a_local_lo = a.a_local_hi = 0;
+      a.m_rot = f->rank * blk_per_rank;
     } else {
       // every rank walks the shards in the same order, so shard s is complete everywhere
       // after (s+1)/nranks of the run and its owner can reduce it while the rest computes

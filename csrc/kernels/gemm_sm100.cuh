@@ -135,9 +135,18 @@ __device__ void comm_allgather_push(const Args& a, int cta, int nctas) {
     const size_t n16 = static_cast<size_t>(rows) * row_bytes / 16;
     const char* src = static_cast<const char*>(c.a_local) + off;
     if (c.use_multimem) {
+      // eight independent loads in flight per thread: the stores are fire-and-forget, the
+      // local loads are what has to be overlapped
       char* dst = static_cast<char*>(c.a_full_mc) + shard_off + off;
-      for (size_t i = threadIdx.x; i < n16; i += blockDim.x)
-        ptx::multimem_st_v4(dst + i * 16, ptx::ld_global_v4(src + i * 16));
+      size_t i = threadIdx.x;
+      for (; i + 7 * blockDim.x < n16; i += 8 * blockDim.x) {
+        uint4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = ptx::ld_global_v4(src + (i + u * blockDim.x) * 16);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) ptx::multimem_st_v4(dst + (i + u * blockDim.x) * 16, v[u]);
+      }
+      for (; i < n16; i += blockDim.x) ptx::multimem_st_v4(dst + i * 16, ptx::ld_global_v4(src + i * 16));
     } else {
       for (size_t i = threadIdx.x; i < n16; i += blockDim.x) {
         const uint4 v = ptx::ld_global_v4(src + i * 16);
@@ -181,7 +190,24 @@ __device__ void comm_reduce_scatter(const Args& a, int cta, int nctas) {
     const size_t src_off = (static_cast<size_t>(c.rank) * c.rows_per_rank + b * BM) * row_bytes;
     const size_t per_row16 = row_bytes / 16;
     const size_t n16 = static_cast<size_t>(rows) * per_row16;
-    for (size_t i = threadIdx.x; i < n16; i += blockDim.x) {
+    char* out_base = static_cast<char*>(c.rs_out) + static_cast<size_t>(b) * BM * static_cast<size_t>(c.rs_ldo) * 2;
+    size_t i0 = threadIdx.x;
+    if (c.use_multimem) {
+      // in-switch reduction: eight requests in flight per thread hide the switch round trip
+      for (; i0 + 7 * blockDim.x < n16; i0 += 8 * blockDim.x) {
+        uint4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          v[u] = ptx::multimem_ld_reduce_bf16x8(static_cast<const char*>(c.c_part_mc) + src_off + (i0 + u * blockDim.x) * 16);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const size_t i = i0 + u * blockDim.x;
+          const size_t r = i / per_row16, col16 = i - r * per_row16;
+          ptx::st_global_v4(out_base + r * static_cast<size_t>(c.rs_ldo) * 2 + col16 * 16, v[u]);
+        }
+      }
+    }
+    for (size_t i = i0; i < n16; i += blockDim.x) {
       const size_t r = i / per_row16, col16 = i - r * per_row16;
       uint4 out;
       if (c.use_multimem) {

@@ -122,6 +122,7 @@ ucclResult_t SymHeap::allocVmm(size_t size, SymSegment* seg) {
   mcProp.size = mapSize;
 
   bool ok = true;
+  UCCL_LOG(TRACE, "symmem: cuMemCreate %zu bytes (granularity %zu)", mapSize, gran);
   CU_TRY(d.memCreate(&seg->handle, mapSize, &prop, 0), ok = false);
   if (!agree(ok)) {
     if (ok) d.memRelease(seg->handle);
@@ -183,6 +184,7 @@ ucclResult_t SymHeap::allocVmm(size_t size, SymSegment* seg) {
         if (!mapHandle(seg->peerHandle[i], &seg->peer[i])) ok = false;
       }
   }
+  UCCL_LOG(TRACE, "symmem: peer handles mapped ok=%d", (int)ok);
   // keep myFd open until every peer imported it
   const bool allOk = agree(ok);
   if (myFd >= 0) ::close(myFd);
@@ -220,11 +222,13 @@ ucclResult_t SymHeap::allocVmm(size_t size, SymSegment* seg) {
     mok = agree(mok);
     if (mcFd >= 0) ::close(mcFd);
     if (mok) CU_TRY(d.multicastAddDevice(seg->mcHandle, dev_), mok = false);
+    UCCL_LOG(TRACE, "symmem: multicast device added ok=%d", (int)mok);
     mok = agree(mok);  // every device must be added before anybody binds
     if (mok) {
       CU_TRY(d.multicastBindMem(seg->mcHandle, 0, seg->handle, 0, mapSize, 0), mok = false);
       if (mok) seg->mcBound = true;
     }
+    UCCL_LOG(TRACE, "symmem: multicast bound ok=%d", (int)mok);
     mok = agree(mok);
     if (mok) {
       if (!mapHandle(seg->mcHandle, &seg->mc)) mok = false;

@@ -229,6 +229,57 @@ PYBIND11_MODULE(_uccl_bindings, m) {
         py::arg("A"), py::arg("B"), py::arg("C"), py::arg("M"), py::arg("N"), py::arg("K"), py::arg("lda"),
         py::arg("ldb"), py::arg("ldc"), py::arg("epilogue") = 0, py::arg("stream") = 0);
 
+  // ---------------------------------------------------------------- fused kernels
+  m.def("allreduce_residual_rmsnorm",
+        [](uintptr_t c, uintptr_t x, uintptr_t residual, uintptr_t gamma, uintptr_t out, uintptr_t residualOut, int tokens,
+           int hidden, float eps, uintptr_t stream) {
+          check(ucclAllReduceResidualRMSNorm(P(x), P(residual), P(gamma), P(out), P(residualOut), tokens, hidden, eps, C(c),
+                                             P(stream)),
+                "ucclAllReduceResidualRMSNorm", C(c));
+        }, nogil());
+  m.def("allgather_gemm",
+        [](uintptr_t c, uintptr_t xShard, uintptr_t xFull, uintptr_t W, uintptr_t out, int M, int N, int K, int epilogue,
+           uintptr_t stream) {
+          check(ucclAllGatherGemm(P(xShard), P(xFull), P(W), P(out), M, N, K, epilogue, C(c), P(stream)), "ucclAllGatherGemm", C(c));
+        }, nogil());
+  m.def("gemm_reduce_scatter",
+        [](uintptr_t c, uintptr_t A, uintptr_t W, uintptr_t cPartial, uintptr_t out, int M, int N, int K, uintptr_t stream) {
+          check(ucclGemmReduceScatter(P(A), P(W), P(cPartial), P(out), M, N, K, C(c), P(stream)), "ucclGemmReduceScatter", C(c));
+        }, nogil());
+
+  // ---------------------------------------------------------------- one-sided windows
+  m.def("window_register", [](uintptr_t c, uintptr_t buf, size_t size) {
+    ucclWindow_t w = nullptr;
+    check(ucclCommWindowRegister(&w, P(buf), size, C(c)), "ucclCommWindowRegister", C(c));
+    return reinterpret_cast<uintptr_t>(w);
+  }, nogil());
+  m.def("window_deregister", [](uintptr_t w) {
+    check(ucclCommWindowDeregister(reinterpret_cast<ucclWindow_t>(w)), "ucclCommWindowDeregister");
+  }, nogil());
+  m.def("put", [](uintptr_t c, uintptr_t local, size_t count, int dt, int peer, uintptr_t win, size_t off, uintptr_t stream) {
+    check(ucclPut(P(local), count, DT(dt), peer, reinterpret_cast<ucclWindow_t>(win), off, C(c), P(stream)), "ucclPut", C(c));
+  }, nogil());
+  m.def("get", [](uintptr_t c, uintptr_t local, size_t count, int dt, int peer, uintptr_t win, size_t off, uintptr_t stream) {
+    check(ucclGet(P(local), count, DT(dt), peer, reinterpret_cast<ucclWindow_t>(win), off, C(c), P(stream)), "ucclGet", C(c));
+  }, nogil());
+  m.def("put_signal", [](uintptr_t c, uintptr_t local, size_t count, int dt, int peer, uintptr_t win, size_t off, uintptr_t stream) {
+    check(ucclPutSignal(P(local), count, DT(dt), peer, reinterpret_cast<ucclWindow_t>(win), off, 0, 0, 0, C(c), P(stream)),
+          "ucclPutSignal", C(c));
+  }, nogil());
+  m.def("get_signal", [](uintptr_t c, uintptr_t local, size_t count, int dt, int peer, uintptr_t win, size_t off, uintptr_t stream) {
+    check(ucclGetSignal(P(local), count, DT(dt), peer, reinterpret_cast<ucclWindow_t>(win), off, 0, 0, 0, C(c), P(stream)),
+          "ucclGetSignal", C(c));
+  }, nogil());
+  m.def("signal", [](uintptr_t c, int peer, uintptr_t stream) {
+    check(ucclSignal(peer, 0, 0, 0, C(c), P(stream)), "ucclSignal", C(c));
+  }, nogil());
+  m.def("wait_signal", [](uintptr_t c, uintptr_t win, const std::vector<int>& peers, const std::vector<int>& counts, uintptr_t stream) {
+    if (peers.size() != counts.size() || peers.size() > 8) throw std::invalid_argument("need 1..8 (peer, count) pairs");
+    ucclWaitSignalDesc_t d[8];
+    for (size_t i = 0; i < peers.size(); ++i) d[i] = {counts[i], peers[i], 0, 0, reinterpret_cast<ucclWindow_t>(win)};
+    check(ucclWaitSignal(static_cast<int>(peers.size()), d, C(c), P(stream)), "ucclWaitSignal", C(c));
+  }, nogil());
+
   // ---------------------------------------------------------------- native self tests
   m.def("selftest_names", [] {
     std::vector<std::string> out;

@@ -1,0 +1,74 @@
+"""Multi-GPU tests: one process per GPU over NVLink.  Need >= 2 devices."""
+import pytest
+import torch
+
+from mp_util import assert_all_ok, run_ranks
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+
+def _n():
+    n = torch.cuda.device_count()
+    return 8 if n >= 8 else (4 if n >= 4 else 2)
+
+
+def test_allreduce_config1_on_gpus():
+    res = run_ranks("allreduce_config1", 2)
+    assert_all_ok(res)
+
+
+def test_collective_matrix():
+    assert_all_ok(run_ranks("collectives_small", _n(), timeout=300))
+
+
+def test_collective_matrix_symmetric_buffers():
+    assert_all_ok(run_ranks("collectives_symmetric", _n(), timeout=300))
+
+
+def test_allreduce_every_algorithm():
+    res = run_ranks("allreduce_algos", _n(), timeout=400)
+    assert_all_ok(res)
+    hist = res[0]["algo_hist"]
+    # ring, one-shot, two-shot and copy-engine all ran (NVLS only where the fabric has it)
+    assert hist[1] > 0 and hist[2] > 0 and hist[3] > 0 and hist[5] > 0
+    if res[0]["nvls"]:
+        assert hist[4] > 0
+
+
+def test_sendrecv():
+    assert_all_ok(run_ranks("sendrecv", _n()))
+
+
+def test_rma_put_get_signal():
+    assert_all_ok(run_ranks("rma", _n()))
+
+
+def test_fused_allreduce_residual_rmsnorm():
+    assert_all_ok(run_ranks("fused_norm", _n()))
+
+
+def test_tensor_parallel_mlp():
+    assert_all_ok(run_ranks("tp_mlp", _n(), timeout=300))
+
+
+def test_network_path_on_gpus():
+    """UCCL_FORCE_NET=1: persistent ring kernel <-> mapped FIFO <-> proxy <-> socket plugin."""
+    res = run_ranks("collectives_small", 2, env={"UCCL_FORCE_NET": "1"}, timeout=300)
+    assert_all_ok(res)
+    assert res[0]["algo_hist"][6] > 0
+
+
+def test_skipped_collective_reports_timeout():
+    env = {"UCCL_WAIT_TIMEOUT_MS": "800", "UCCL_NVLS": "0"}
+    res = run_ranks("skipped_collective", 2, env=env, timeout=120)
+    for r in res:
+        assert "died" not in r and not r["fail"], r
+    assert res[0]["timeouts"] >= 1 and res[0]["seconds"] < 30
+    assert "wait expired" in res[0]["last"] or "remote" in (res[0]["err"] or "").lower()
+
+
+def test_rank_that_exits_between_steps():
+    env = {"UCCL_WAIT_TIMEOUT_MS": "800", "UCCL_NVLS": "0"}
+    res = run_ranks("peer_exits", 2, env=env, timeout=120)
+    assert "died" not in res[0] and not res[0]["fail"], res[0]
+    assert res[0]["seconds"] < 30

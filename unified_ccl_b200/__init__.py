@@ -18,6 +18,6 @@ except ImportError as _e:  # pragma: no cover - exercised only on a broken check
 
 __version__ = "0.1.0"
 
-from .communicator import Communicator, get_unique_id  # noqa: E402,F401
+from .communicator import Communicator, Window, get_unique_id  # noqa: E402,F401
 
-__all__ = ["Communicator", "get_unique_id"]
+__all__ = ["Communicator", "Window", "get_unique_id"]

@@ -329,3 +329,50 @@ def _tensor_from_ptr(ptr: int, numel: int, dtype, device_index: int) -> torch.Te
     itemsize = torch.empty((), dtype=dtype).element_size()
     raw = torch.as_tensor(_CudaArray(ptr, max(numel * itemsize, 1)), device=torch.device("cuda", device_index))
     return raw[: numel * itemsize].view(dtype)
+
+
+class Window:
+    """A registered buffer that peers can put into / get from, with per-peer signal counters.
+
+    Collective: every rank registers a tensor of the same size.  Signal counters are monotonic;
+    ``wait_signal`` takes the absolute number of signals expected from a peer so far (the
+    semantics of the reference's ucclWaitSignal, src/rma/rma.cc:474-570).
+    """
+
+    def __init__(self, comm: Communicator, tensor: torch.Tensor):
+        comm._check(tensor)
+        self._comm = comm
+        self.tensor = tensor
+        self._win = _C.window_register(comm.handle, tensor.data_ptr(), tensor.numel() * tensor.element_size())
+
+    def _args(self, local: torch.Tensor, peer: int, offset_elems: int):
+        self._comm._check(local)
+        if local.dtype != self.tensor.dtype:
+            raise TypeError("dtype differs from the window's")
+        return (self._comm.handle, local.data_ptr(), local.numel(), _DTYPES[local.dtype], peer, self._win,
+                offset_elems * local.element_size(), self._comm._stream())
+
+    def put(self, local, peer, offset=0):
+        _C.put(*self._args(local, peer, offset))
+
+    def get(self, local, peer, offset=0):
+        _C.get(*self._args(local, peer, offset))
+
+    def put_signal(self, local, peer, offset=0):
+        _C.put_signal(*self._args(local, peer, offset))
+
+    def get_signal(self, local, peer, offset=0):
+        _C.get_signal(*self._args(local, peer, offset))
+
+    def signal(self, peer):
+        _C.signal(self._comm.handle, peer, self._comm._stream())
+
+    def wait_signal(self, peers, counts):
+        if isinstance(peers, int):
+            peers, counts = [peers], [counts]
+        _C.wait_signal(self._comm.handle, self._win, list(peers), list(counts), self._comm._stream())
+
+    def close(self):
+        if self._win:
+            win, self._win = self._win, 0
+            _C.window_deregister(win)
