@@ -175,7 +175,7 @@ extern "C" ucclResult_t ucclAllGatherGemm(const void* xShard, void* xFull, const
   f.role = 1;
   f.rank = c->localRank;
   f.nranks = n;
-  f.comm_ctas = c->cfg.maxCtas > 0 ? std::min(c->cfg.maxCtas, 32) : 16;
+  f.comm_ctas = c->cfg.maxCtas > 0 ? std::min(c->cfg.maxCtas, 32) : 8;
   f.epoch = 1;
   f.timeout_ns = c->dev.timeoutNs;
   f.abort_flag = c->dev.abortFlag;
@@ -232,7 +232,7 @@ extern "C" ucclResult_t ucclGemmReduceScatter(const void* A, const void* W, void
   f.role = 2;
   f.rank = c->localRank;
   f.nranks = n;
-  f.comm_ctas = c->cfg.maxCtas > 0 ? std::min(c->cfg.maxCtas, 32) : 16;
+  f.comm_ctas = c->cfg.maxCtas > 0 ? std::min(c->cfg.maxCtas, 32) : 8;
   f.epoch = 1;
   f.timeout_ns = c->dev.timeoutNs;
   f.abort_flag = c->dev.abortFlag;

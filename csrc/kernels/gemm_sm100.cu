@@ -98,7 +98,7 @@ ucclResult_t launchGemmBf16(const GemmLaunch& g, const GemmFusion* f, cudaStream
   int role = f ? f->role : 0;
   int comm_ctas = 0;
   if (role != 0) {
-    comm_ctas = f->comm_ctas > 0 ? f->comm_ctas : 16;
+    comm_ctas = f->comm_ctas > 0 ? f->comm_ctas : 8;
     if (comm_ctas > sms / 2) comm_ctas = sms / 2;
     gemm::CommArgs& c = a.comm;
     c.rank = f->rank;
@@ -125,13 +125,13 @@ ucclResult_t launchGemmBf16(const GemmLaunch& g, const GemmFusion* f, cudaStream
       a.a_ready = f->ready_peer[f->rank];
       a.a_ready_target = f->epoch;
       // the local shard is copied into A_full by the communication CTAs as well, so its rows
-      // are awaited like everybody else's; they simply arrive first, hence the rotation
+      // are awaited like everybody else's; they simply arrive first
       a.a_local_lo = a.a_local_hi = 0;
-      a.m_rot = f->rank * blk_per_rank;
+      a.m_order = 1;
+      a.m_bpr = blk_per_rank;
     } else {
-      // every rank walks the shards in the same order, so shard s is complete everywhere
-      // after (s+1)/nranks of the run and its owner can reduce it while the rest computes
-      a.m_rot = 0;
+      a.m_order = 2;
+      a.m_bpr = blk_per_rank;
     }
   }
   int gemm_ctas = sms - comm_ctas;

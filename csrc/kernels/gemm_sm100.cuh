@@ -79,6 +79,8 @@ struct Args {
   int tiles_m, tiles_n;
   int gemm_ctas;            // CTAs [0, gemm_ctas) run the GEMM roles
   int m_rot;                // row-block rotation: logical block i maps to (i + m_rot) % tiles_m
+  int m_order;              // 0: rotation only; 1: all-gather order; 2: reduce-scatter order
+  int m_bpr;                // row blocks per rank shard (fused modes)
   int b_half_rows;          // SwiGLU: row offset of the "up" half inside B; plain: unused
   const uint32_t* a_ready;  // optional arrival flags per row block (local memory)
   uint32_t a_ready_target;
@@ -96,8 +98,26 @@ __device__ __forceinline__ void tile_coords(const Args& a, int tile, int& mb, in
   const int r = tile - g * per_group;
   int m = first + (r % gsz);
   nb = r / gsz;
-  m += a.m_rot;
-  if (m >= a.tiles_m) m -= a.tiles_m;
+  if (a.m_order == 1) {
+    // all-gather: my own shard first (it is already here), then row block j of every other
+    // shard for j = 0, 1, ... -- the order in which the peers' pushes arrive
+    const int bpr = a.m_bpr, n = a.comm.nranks, r = a.comm.rank;
+    if (m < bpr) {
+      m = r * bpr + m;
+    } else {
+      const int i = m - bpr, j = i / (n - 1), q = i % (n - 1) + 1;
+      m = ((r + q) % n) * bpr + j;
+    }
+  } else if (a.m_order == 2) {
+    // reduce-scatter: row block j of every shard in turn, so that every owner can reduce its
+    // rows steadily while the GEMM runs instead of all at once at the end
+    const int bpr = a.m_bpr, n = a.comm.nranks;
+    const int j = m / n, s = (m % n + a.comm.rank) % n;
+    m = s * bpr + j;
+  } else {
+    m += a.m_rot;
+    if (m >= a.tiles_m) m -= a.tiles_m;
+  }
   mb = m;
 }
 
@@ -193,14 +213,14 @@ __device__ void comm_reduce_scatter(const Args& a, int cta, int nctas) {
     char* out_base = static_cast<char*>(c.rs_out) + static_cast<size_t>(b) * BM * static_cast<size_t>(c.rs_ldo) * 2;
     size_t i0 = threadIdx.x;
     if (c.use_multimem) {
-      // in-switch reduction: eight requests in flight per thread hide the switch round trip
-      for (; i0 + 7 * blockDim.x < n16; i0 += 8 * blockDim.x) {
-        uint4 v[8];
+      // in-switch reduction: sixteen requests in flight per thread hide the switch round trip
+      for (; i0 + 15 * blockDim.x < n16; i0 += 16 * blockDim.x) {
+        uint4 v[16];
 #pragma unroll
-        for (int u = 0; u < 8; ++u)
+        for (int u = 0; u < 16; ++u)
           v[u] = ptx::multimem_ld_reduce_bf16x8(static_cast<const char*>(c.c_part_mc) + src_off + (i0 + u * blockDim.x) * 16);
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
+        for (int u = 0; u < 16; ++u) {
           const size_t i = i0 + u * blockDim.x;
           const size_t r = i / per_row16, col16 = i - r * per_row16;
           ptx::st_global_v4(out_base + r * static_cast<size_t>(c.rs_ldo) * 2 + col16 * 16, v[u]);

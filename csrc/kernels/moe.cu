@@ -57,13 +57,14 @@ __global__ void __launch_bounds__(kMoeThreads) moe_dispatch_kernel(const __grid_
         for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
 #pragma unroll
         for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        // x / scale with a true division: bit-identical to the fp32 restatement of the cast, so
+        // no element lands on the other side of an fp8 rounding boundary
         const float scale = fmaxf(amax, 1e-10f) / 448.f;
-        const float inv = 1.f / scale;
         uint32_t lo = 0, hi = 0;
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
-          const __nv_fp8x2_storage_t a0 = __nv_cvt_float2_to_fp8x2(make_float2(f[4 * j] * inv, f[4 * j + 1] * inv), __NV_SATFINITE, __NV_E4M3);
-          const __nv_fp8x2_storage_t a1 = __nv_cvt_float2_to_fp8x2(make_float2(f[4 * j + 2] * inv, f[4 * j + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+          const __nv_fp8x2_storage_t a0 = __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(f[4 * j], scale), __fdiv_rn(f[4 * j + 1], scale)), __NV_SATFINITE, __NV_E4M3);
+          const __nv_fp8x2_storage_t a1 = __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(f[4 * j + 2], scale), __fdiv_rn(f[4 * j + 3], scale)), __NV_SATFINITE, __NV_E4M3);
           const uint32_t word = static_cast<uint32_t>(a0) | (static_cast<uint32_t>(a1) << 16);
           if (j == 0) lo = word; else hi = word;
         }

@@ -247,6 +247,40 @@ PYBIND11_MODULE(_uccl_bindings, m) {
           check(ucclGemmReduceScatter(P(A), P(W), P(cPartial), P(out), M, N, K, C(c), P(stream)), "ucclGemmReduceScatter", C(c));
         }, nogil());
 
+  // ---------------------------------------------------------------- MoE dispatch / combine
+  m.def("moe_create", [](uintptr_t c, int maxTokens, int hidden, int experts, int topk, float factor) {
+    ucclMoeContext_t ctx = nullptr;
+    check(ucclMoeCreate(&ctx, maxTokens, hidden, experts, topk, factor, C(c)), "ucclMoeCreate", C(c));
+    return reinterpret_cast<uintptr_t>(ctx);
+  }, nogil());
+  m.def("moe_destroy", [](uintptr_t ctx) { check(ucclMoeDestroy(reinterpret_cast<ucclMoeContext_t>(ctx)), "ucclMoeDestroy"); }, nogil());
+  m.def("moe_layout", [](uintptr_t ctx) {
+    ucclMoeLayout_t l;
+    check(ucclMoeGetLayout(reinterpret_cast<ucclMoeContext_t>(ctx), &l), "ucclMoeGetLayout");
+    py::dict d;
+    d["recv_x"] = reinterpret_cast<uintptr_t>(l.recvX);
+    d["recv_scale"] = reinterpret_cast<uintptr_t>(l.recvScale);
+    d["recv_meta"] = reinterpret_cast<uintptr_t>(l.recvMeta);
+    d["recv_counts"] = reinterpret_cast<uintptr_t>(l.recvCounts);
+    d["expert_out"] = reinterpret_cast<uintptr_t>(l.expertOut);
+    d["rows_per_source"] = l.rowsPerSource;
+    d["nranks"] = l.nranks;
+    return d;
+  });
+  m.def("moe_dispatch", [](uintptr_t ctx, uintptr_t x, uintptr_t idx, int tokens, uintptr_t stream) {
+    check(ucclMoeDispatch(reinterpret_cast<ucclMoeContext_t>(ctx), P(x), static_cast<const int32_t*>(P(idx)), tokens, P(stream)),
+          "ucclMoeDispatch");
+  }, nogil());
+  m.def("moe_combine", [](uintptr_t ctx, uintptr_t w, int tokens, uintptr_t out, uintptr_t stream) {
+    check(ucclMoeCombine(reinterpret_cast<ucclMoeContext_t>(ctx), static_cast<const float*>(P(w)), tokens, P(out), P(stream)),
+          "ucclMoeCombine");
+  }, nogil());
+  m.def("moe_overflow", [](uintptr_t ctx) {
+    unsigned int rows = 0;
+    check(ucclMoeOverflow(reinterpret_cast<ucclMoeContext_t>(ctx), &rows), "ucclMoeOverflow");
+    return rows;
+  });
+
   // ---------------------------------------------------------------- one-sided windows
   m.def("window_register", [](uintptr_t c, uintptr_t buf, size_t size) {
     ucclWindow_t w = nullptr;

@@ -202,24 +202,40 @@ ucclResult_t ucclAllGatherGemm(const void* xShard, void* xFull, const void* W, v
 ucclResult_t ucclGemmReduceScatter(const void* A, const void* W, void* cPartial, void* out, int M,
                                    int N, int K, ucclComm_t comm, void* stream);
 
-/* MoE expert-parallel all-to-all.  See uccl_moe section in the user guide. */
+/* MoE expert-parallel all-to-all (experts are spread evenly: rank r owns experts
+ * [r * E / nranks, (r + 1) * E / nranks)).
+ *
+ * Dispatch sends every (token, k) pair to the rank that owns expert topkIdx[token][k]: the row is
+ * converted from bf16 to fp8 e4m3 with one fp32 scale per 128 elements on the way.  Each source
+ * rank owns a fixed region of `rowsPerSource` rows on every destination, so the receive area is
+ * [nranks][rowsPerSource] rows and recvCounts[s] tells how many rows of region s are valid.
+ * The caller runs its experts on the received rows and writes one bf16 output row per received
+ * row, at the same index, into `expertOut`.  Combine then pulls, for every local token, its topk
+ * output rows from the ranks that produced them and writes out = sum_k weight[k] * row_k. */
 typedef struct ucclMoeContext* ucclMoeContext_t;
-ucclResult_t ucclMoeCreate(ucclMoeContext_t* ctx, int maxTokensPerRank, int hidden, int numExperts,
-                           int topk, ucclComm_t comm);
+typedef struct {
+  void* recvX;          /* fp8 e4m3 [nranks][rowsPerSource][hidden]                     */
+  float* recvScale;     /* fp32     [nranks][rowsPerSource][hidden / 128]               */
+  int32_t* recvMeta;    /* int32    [nranks][rowsPerSource][4]: source token, local expert, k, 1 */
+  int32_t* recvCounts;  /* int32    [nranks] valid rows per source region               */
+  void* expertOut;      /* bf16     [nranks][rowsPerSource][hidden], written by the caller */
+  int rowsPerSource;
+  int nranks;
+} ucclMoeLayout_t;
+/* Collective.  capacityFactor <= 0 sizes the regions for the worst case
+ * (maxTokensPerRank * min(topk, numExperts / nranks) rows per source); a positive factor sizes
+ * them to factor * maxTokensPerRank * topk / nranks rows and rows beyond that are dropped and
+ * counted (ucclMoeOverflow). */
+ucclResult_t ucclMoeCreate(ucclMoeContext_t* ctx, int maxTokensPerRank, int hidden, int numExperts, int topk,
+                           float capacityFactor, ucclComm_t comm);
 ucclResult_t ucclMoeDestroy(ucclMoeContext_t ctx);
-/* x [tokens, hidden] bf16, topkIdx [tokens, topk] int32 (global expert ids).
- * Outputs live in the context's symmetric receive area:
- *   recvX      fp8 e4m3 [capacity, hidden]      (capacity = nranks * maxTokensPerRank)
- *   recvScale  fp32     [capacity, hidden/128]
- *   recvMeta   int32    [capacity, 4]           (src rank, src token, local expert, k slot)
- *   recvCount  int32    [1]                     rows received by this rank            */
-ucclResult_t ucclMoeDispatch(ucclMoeContext_t ctx, const void* x, const int32_t* topkIdx,
-                             int tokens, void** recvX, void** recvScale, int32_t** recvMeta,
-                             int32_t** recvCount, void* stream);
-/* y [rows received, hidden] bf16 expert outputs in the order of recvX; topkWeight [tokens, topk]
- * fp32; out [tokens, hidden] bf16 = sum_k w_k * y_k. */
-ucclResult_t ucclMoeCombine(ucclMoeContext_t ctx, const void* y, const float* topkWeight,
-                            int tokens, void* out, void* stream);
+ucclResult_t ucclMoeGetLayout(ucclMoeContext_t ctx, ucclMoeLayout_t* layout);
+/* x [tokens, hidden] bf16, topkIdx [tokens, topk] int32 global expert ids (negative = unused). */
+ucclResult_t ucclMoeDispatch(ucclMoeContext_t ctx, const void* x, const int32_t* topkIdx, int tokens, void* stream);
+/* topkWeight [tokens, topk] fp32; out [tokens, hidden] bf16.  Uses the routing of the last dispatch. */
+ucclResult_t ucclMoeCombine(ucclMoeContext_t ctx, const float* topkWeight, int tokens, void* out, void* stream);
+/* Rows dropped so far because a region was full (always 0 with capacityFactor <= 0). */
+ucclResult_t ucclMoeOverflow(ucclMoeContext_t ctx, unsigned int* rows);
 
 /* ==================================================================
  * extensions: tuning, introspection, counters

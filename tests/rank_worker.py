@@ -349,6 +349,66 @@ def case_rma(comm, rank, n, args):
     return {"fail": fail}
 
 
+def case_moe(comm, rank, n, args):
+    from unified_ccl_b200.parallel import MoeDispatcher, quantize_fp8_block128
+
+    dev = _dev(comm, rank)
+    fail = []
+    for hidden, experts, topk, max_tokens in ((1024, 8 * n, 4, 192), (7168, 32 * n, 8, 96)):
+        eloc = experts // n
+        disp = MoeDispatcher(comm, max_tokens, hidden, experts, topk)
+
+        def inputs(r):
+            g = torch.Generator().manual_seed(500 + r)
+            t = max_tokens - 3 * r
+            x = torch.randn(t, hidden, generator=g).to(torch.bfloat16)
+            logits = torch.randn(t, experts, generator=g)
+            w, idx = torch.softmax(logits, -1).topk(topk, dim=-1)
+            return x, idx.to(torch.int32), w.float().contiguous()
+
+        everyone = [inputs(r) for r in range(n)]
+        x, idx, w = everyone[rank]
+        for rnd in range(2):  # the second round reuses every buffer and counter
+            rx, rs, rm, rc = disp.dispatch(x.to(dev), idx.to(dev).contiguous())
+            _sync(comm)
+            counts = rc.cpu().tolist()
+            for s in range(n):
+                xs, idxs, _ = everyone[s]
+                want = {(t, int(idxs[t, k]) - rank * eloc, k) for t in range(xs.shape[0]) for k in range(topk)
+                        if int(idxs[t, k]) // eloc == rank}
+                meta = rm[s, :counts[s]].cpu()
+                got = {(int(m[0]), int(m[1]), int(m[2])) for m in meta}
+                if counts[s] != len(want) or got != want or (counts[s] and not (meta[:, 3] == 1).all()):
+                    fail.append(("routing", hidden, rnd, s, counts[s], len(want)))
+                    continue
+                if counts[s] == 0:
+                    continue
+                src_rows = xs[meta[:, 0].long()].float()
+                deq = rx[s, :counts[s]].float().cpu().view(counts[s], hidden // 128, 128) * rs[s, :counts[s]].cpu().unsqueeze(-1)
+                amax = src_rows.view(counts[s], hidden // 128, 128).abs().amax(-1, keepdim=True)
+                bad = ((deq - src_rows.view_as(deq)).abs() > 0.0625 * amax + 1e-6).sum().item()
+                qref, sref = quantize_fp8_block128(src_rows)
+                if bad or not torch.allclose(rs[s, :counts[s]].cpu(), sref, rtol=1e-6, atol=0):
+                    fail.append(("payload", hidden, rnd, s, bad))
+                # the "expert": scale the dequantised row by (global expert id + 1)
+                gid = (meta[:, 1] + rank * eloc + 1).float().unsqueeze(-1)
+                disp.expert_out[s, :counts[s]] = (deq.view(counts[s], hidden) * gid).to(torch.bfloat16).to(dev)
+            out = disp.combine(w.to(dev))
+            _sync(comm)
+            q, sc = quantize_fp8_block128(x.float())
+            deq_x = (q.float().view(x.shape[0], hidden // 128, 128) * sc.unsqueeze(-1)).view(x.shape[0], hidden)
+            ref = torch.zeros(x.shape[0], hidden)
+            for k in range(topk):
+                ref += w[:, k:k + 1] * (deq_x * (idx[:, k:k + 1].float() + 1)).to(torch.bfloat16).float()
+            err = (out.float().cpu() - ref).abs().max().item()
+            if err > 2e-2 * ref.abs().max().item() + 1e-3:
+                fail.append(("combine", hidden, rnd, err, ref.abs().max().item()))
+        if disp.overflow() != 0:
+            fail.append(("overflow", hidden))
+        disp.close()
+    return {"fail": fail}
+
+
 def case_skipped_collective(comm, rank, n, args):
     """The last rank skips one all-reduce: the others' device-side waits run out and report it."""
     dev = _dev(comm, rank)

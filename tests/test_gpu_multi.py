@@ -51,6 +51,10 @@ def test_tensor_parallel_mlp():
     assert_all_ok(run_ranks("tp_mlp", _n(), timeout=300))
 
 
+def test_moe_dispatch_combine():
+    assert_all_ok(run_ranks("moe", _n(), timeout=300))
+
+
 def test_network_path_on_gpus():
     """UCCL_FORCE_NET=1: persistent ring kernel <-> mapped FIFO <-> proxy <-> socket plugin."""
     res = run_ranks("collectives_small", 2, env={"UCCL_FORCE_NET": "1"}, timeout=300)

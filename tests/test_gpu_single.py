@@ -28,6 +28,11 @@ def test_tp_mlp_single_rank():
 
 
 @gpu
+def test_moe_single_rank():
+    assert_all_ok(run_ranks("moe", 1))
+
+
+@gpu
 def test_native_library_is_loaded():
     """The CUDA path must come from this repository's shared objects, not from a fallback."""
     import unified_ccl_b200 as u

@@ -46,7 +46,7 @@ class ClockSampler:
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, gpu_index=0, period_ms=200):
+    def __init__(self, gpu_index=0, period_ms=50):
         self.gpu_index, self.period_ms = gpu_index, period_ms
         self.samples, self._proc, self._thread = [], None, None
 
