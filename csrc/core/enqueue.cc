@@ -426,7 +426,12 @@ TuneChoice chooseFor(Comm* c, ucclCollKind_t kind, size_t bytes, bool symmetric,
   q.forcedAlgo = c->forcedAlgo;
   q.forcedProto = c->forcedProto;
   q.maxBlocks = c->cfg.maxCtas;
-  return c->tuner.choose(q);
+  TuneChoice ch = c->tuner.choose(q);
+  if (c->forcedBlocks > 0) {
+    int cap = (ch.proto == ucclProtoLL || ch.proto == ucclProtoLL128) ? kLLBlocks : kMaxBlocks;
+    ch.blocks = std::min(c->forcedBlocks, cap);
+  }
+  return ch;
 }
 
 ucclResult_t executeOp(const CollOp& op) {

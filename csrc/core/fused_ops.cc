@@ -3,6 +3,7 @@
 // building blocks the library is benchmarked on (a Llama-style MLP block: sequence-parallel
 // activations are gathered in front of the column-parallel up/gate projection and the
 // row-parallel down projection ends in a reduce-scatter).
+#include <stdlib.h>
 #include <string.h>
 
 #include <algorithm>
@@ -41,6 +42,16 @@ ucclResult_t validate(Comm* c) {
     return ucclInvalidUsage;
   }
   return ucclSuccess;
+}
+
+// CTAs that run the communication role of a fused GEMM launch: UCCL_FUSED_COMM_CTAS, else 8.
+int fusedCommCtas(Comm* c) {
+  const char* s = getenv("UCCL_FUSED_COMM_CTAS");
+  if (s && *s) {
+    const int v = atoi(s);
+    if (v >= 1 && v <= 64) return v;
+  }
+  return c->cfg.maxCtas > 0 ? std::min(c->cfg.maxCtas, 32) : 8;
 }
 
 struct Sym {
@@ -175,7 +186,7 @@ extern "C" ucclResult_t ucclAllGatherGemm(const void* xShard, void* xFull, const
   f.role = 1;
   f.rank = c->localRank;
   f.nranks = n;
-  f.comm_ctas = c->cfg.maxCtas > 0 ? std::min(c->cfg.maxCtas, 32) : 8;
+  f.comm_ctas = fusedCommCtas(c);
   f.epoch = 1;
   f.timeout_ns = c->dev.timeoutNs;
   f.abort_flag = c->dev.abortFlag;
@@ -232,7 +243,7 @@ extern "C" ucclResult_t ucclGemmReduceScatter(const void* A, const void* W, void
   f.role = 2;
   f.rank = c->localRank;
   f.nranks = n;
-  f.comm_ctas = c->cfg.maxCtas > 0 ? std::min(c->cfg.maxCtas, 32) : 8;
+  f.comm_ctas = fusedCommCtas(c);
   f.epoch = 1;
   f.timeout_ns = c->dev.timeoutNs;
   f.abort_flag = c->dev.abortFlag;

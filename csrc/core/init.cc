@@ -536,3 +536,10 @@ extern "C" ucclResult_t ucclCommSetAlgo(ucclComm_t comm, ucclAlgo_t algo, ucclPr
   c->forcedProto = proto;
   return ucclSuccess;
 }
+
+extern "C" ucclResult_t ucclCommSetBlocks(ucclComm_t comm, int blocks) {
+  Comm* c = toComm(comm);
+  if (!commValid(c) || blocks < 0 || blocks > kMaxBlocks) return ucclInvalidArgument;
+  c->forcedBlocks = blocks;
+  return ucclSuccess;
+}

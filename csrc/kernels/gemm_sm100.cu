@@ -1,6 +1,11 @@
 // Launchers for the tcgen05 GEMM: tensor-map construction, grid sizing, template dispatch.
 #include "gemm_sm100.h"
 
+#include <stdlib.h>
+#include <string.h>
+
+#include <algorithm>
+
 #include <mutex>
 
 #include "../core/cuda_driver.h"
@@ -63,6 +68,66 @@ cudaError_t launchT(const CUtensorMap& tmA, const CUtensorMap& tmB, const gemm::
   if (attr_err != cudaSuccess) return attr_err;
   kern<<<grid, gemm::NUM_THREADS, gemm::SMEM_BYTES, stream>>>(tmA, tmB, args);
   return cudaGetLastError();
+}
+
+template <int EPI, int COMM>
+cudaError_t launchPairT(const CUtensorMap& tmA, const CUtensorMap& tmB, const gemm::Args& args, int grid,
+                        cudaStream_t stream) {
+  auto kern = gemm::gemm2_bf16_kernel<EPI, COMM>;
+  static thread_local int last_dev = -1;
+  static cudaError_t attr_err = cudaSuccess;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev != last_dev) {
+    attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm::pair::SMEM_BYTES);
+    last_dev = dev;
+  }
+  if (attr_err != cudaSuccess) return attr_err;
+  kern<<<grid, gemm::NUM_THREADS, gemm::pair::SMEM_BYTES, stream>>>(tmA, tmB, args);
+  return cudaGetLastError();
+}
+
+// Clusters of two CTAs that fit on the device at once (one CTA per SM; GPCs with an odd number of
+// usable SMs leave one SM unpaired).
+int maxResidentPairs() {
+  static int cached[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return deviceSmCount() / 2;
+  if (cached[dev] == 0) {
+    auto kern = gemm::gemm2_bf16_kernel<gemm::kEpiStore, gemm::kCommNone>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm::pair::SMEM_BYTES);
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(2 * deviceSmCount(), 1, 1);
+    cfg.blockDim = dim3(gemm::NUM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = gemm::pair::SMEM_BYTES;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
+      (void)cudaGetLastError();
+      n = deviceSmCount() / 2 - 4;
+    }
+    cached[dev] = n;
+    UCCL_LOG(INFO, "gemm: %d CTA pairs can be resident on device %d", n, dev);
+  }
+  return cached[dev];
+}
+
+// UCCL_GEMM_PAIR=0 selects the single-CTA kernel, 1 the CTA-pair kernel (default).
+bool usePairKernel() {
+  static int v = -1;
+  if (v < 0) {
+    const char* s = getenv("UCCL_GEMM_PAIR");
+    v = (s && *s) ? (atoi(s) != 0) : 1;
+  }
+  return v != 0;
 }
 
 }  // namespace
@@ -134,9 +199,43 @@ ucclResult_t launchGemmBf16(const GemmLaunch& g, const GemmFusion* f, cudaStream
       a.m_bpr = blk_per_rank;
     }
   }
+  const bool fusedOk = role == 0 || (f->rows_per_rank % (2 * gemm::BM) == 0);
+  if (usePairKernel() && fusedOk) {
+    // CTA pairs: 256-row tiles, both the GEMM part and the communication part of the grid are even
+    const int tiles_m2 = (g.M + 2 * gemm::BM - 1) / (2 * gemm::BM);
+    const int tiles2 = tiles_m2 * a.tiles_n;
+    if (comm_ctas & 1) ++comm_ctas;
+    // every cluster of the grid must be resident at once: the GEMM CTAs of a fused launch wait
+    // for the communication CTAs of the same launch
+    int maxPairs = maxResidentPairs();
+    if (g.max_ctas > 0) maxPairs = std::min(maxPairs, g.max_ctas / 2);
+    int pairs = maxPairs - comm_ctas / 2;
+    if (pairs > tiles2) pairs = tiles2;
+    if (pairs < 1) pairs = 1;
+    a.gemm_ctas = 2 * pairs;
+    a.comm_ctas = comm_ctas;
+    const int grid2 = a.gemm_ctas + comm_ctas;
+    cudaError_t e2;
+    if (g.epilogue == gemm::kEpiSwiGLU) {
+      if (role == gemm::kCommAllGatherPush) e2 = launchPairT<gemm::kEpiSwiGLU, gemm::kCommAllGatherPush>(tmA, tmB, a, grid2, stream);
+      else if (role == 0) e2 = launchPairT<gemm::kEpiSwiGLU, gemm::kCommNone>(tmA, tmB, a, grid2, stream);
+      else return ucclInvalidArgument;
+    } else {
+      if (role == gemm::kCommAllGatherPush) e2 = launchPairT<gemm::kEpiStore, gemm::kCommAllGatherPush>(tmA, tmB, a, grid2, stream);
+      else if (role == gemm::kCommReduceScatter) e2 = launchPairT<gemm::kEpiStore, gemm::kCommReduceScatter>(tmA, tmB, a, grid2, stream);
+      else e2 = launchPairT<gemm::kEpiStore, gemm::kCommNone>(tmA, tmB, a, grid2, stream);
+    }
+    if (e2 != cudaSuccess) {
+      UCCL_LOG(ERROR, "gemm (CTA pair) launch failed: %s", cudaGetErrorString(e2));
+      return ucclSystemError;
+    }
+    return ucclSuccess;
+  }
+
   int gemm_ctas = sms - comm_ctas;
   if (gemm_ctas > tiles) gemm_ctas = tiles;
   a.gemm_ctas = gemm_ctas;
+  a.comm_ctas = comm_ctas;
   const int grid = gemm_ctas + comm_ctas;
 
   cudaError_t e;

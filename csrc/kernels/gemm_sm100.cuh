@@ -77,7 +77,8 @@ struct Args {
   __nv_bfloat16* C;
   int ldc;
   int tiles_m, tiles_n;
-  int gemm_ctas;            // CTAs [0, gemm_ctas) run the GEMM roles
+  int gemm_ctas;            // number of CTAs that run the GEMM roles
+  int comm_ctas;            // CTAs [0, comm_ctas) run the communication role (scheduled first)
   int m_rot;                // row-block rotation: logical block i maps to (i + m_rot) % tiles_m
   int m_order;              // 0: rotation only; 1: all-gather order; 2: reduce-scatter order
   int m_bpr;                // row blocks per rank shard (fused modes)
@@ -262,13 +263,12 @@ template <int EPI, int COMM>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const Args a) {
-  if (COMM != kCommNone && static_cast<int>(blockIdx.x) >= a.gemm_ctas) {
-    const int cta = blockIdx.x - a.gemm_ctas;
-    const int nctas = gridDim.x - a.gemm_ctas;
-    if (COMM == kCommAllGatherPush) comm_allgather_push(a, cta, nctas);
-    if (COMM == kCommReduceScatter) comm_reduce_scatter(a, cta, nctas);
+  if (COMM != kCommNone && static_cast<int>(blockIdx.x) < a.comm_ctas) {
+    if (COMM == kCommAllGatherPush) comm_allgather_push(a, blockIdx.x, a.comm_ctas);
+    if (COMM == kCommReduceScatter) comm_reduce_scatter(a, blockIdx.x, a.comm_ctas);
     return;
   }
+  const int cta_id = (COMM != kCommNone) ? static_cast<int>(blockIdx.x) - a.comm_ctas : static_cast<int>(blockIdx.x);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -313,7 +313,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t it = 0;
-      for (int tile = blockIdx.x; tile < num_tiles && !*bail; tile += gemm_ctas) {
+      for (int tile = cta_id; tile < num_tiles && !*bail; tile += gemm_ctas) {
         int mb, nb;
         tile_coords(a, tile, mb, nb);
         if (a.a_ready && !(mb >= a.a_local_lo && mb < a.a_local_hi)) {
@@ -352,7 +352,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (lane == 0) {
       constexpr uint32_t idesc = ptx::umma_idesc_f16(1u, BM, BN);
       uint32_t it = 0, tcount = 0;
-      for (int tile = blockIdx.x; tile < num_tiles && !*bail; tile += gemm_ctas, ++tcount) {
+      for (int tile = cta_id; tile < num_tiles && !*bail; tile += gemm_ctas, ++tcount) {
         const uint32_t acc = tcount & 1, acc_ph = (tcount >> 1) & 1;
         if (!ptx::mbar_wait_bounded(&tempty_bar[acc], acc_ph ^ 1, bail)) break;
         ptx::tc_fence_after();
@@ -379,7 +379,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ------------------------------------------------------------ epilogue warps
     const int q = warp & 3;  // TMEM lane quarter this warp may access
     uint32_t tcount = 0;
-    for (int tile = blockIdx.x; tile < num_tiles && !*bail; tile += gemm_ctas, ++tcount) {
+    for (int tile = cta_id; tile < num_tiles && !*bail; tile += gemm_ctas, ++tcount) {
       int mb, nb;
       tile_coords(a, tile, mb, nb);
       const uint32_t acc = tcount & 1, acc_ph = (tcount >> 1) & 1;
@@ -469,6 +469,266 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     ptx::tmem_dealloc(tmem_base, TMEM_COLS);
   }
   if (threadIdx.x == 0 && *bail && a.err) atomicCAS(a.err, 0u, 0x47454d4du);
+}
+
+
+// ------------------------------------------------------------------ CTA-pair variant
+// Two CTAs of a cluster share one 256 x 256 output tile (tcgen05 cta_group::2): each CTA stages
+// its own 128 A rows and one half (128 rows) of the B tile, the leader CTA issues one MMA that
+// reads both CTAs' shared memory, and each CTA's TMEM receives the accumulator rows of its own
+// A rows.  Compared with the single-CTA kernel the B operand is fetched once per 256 output rows
+// instead of once per 128, which cuts shared-memory fill traffic by a third and frees room for
+// six pipeline stages.  No load is replicated across the cluster: every TMA copy writes only the
+// shared memory of the CTA that issued it.
+namespace pair {
+constexpr int STAGES = 6;
+constexpr int A_BYTES = BM * BK * 2;          // 16 KiB: this CTA's 128 rows of A
+constexpr int B_BYTES = (BN / 2) * BK * 2;    // 16 KiB: this CTA's half of the B tile
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+}  // namespace pair
+
+// logical 256-row block -> physical 256-row block for the fused orders (see tile_coords)
+__device__ __forceinline__ void pair_tile_coords(const Args& a, int tile, int tiles_m2, int& mb2, int& nb) {
+  constexpr int GROUP_M = 8;
+  const int per_group = GROUP_M * a.tiles_n;
+  const int g = tile / per_group;
+  const int first = g * GROUP_M;
+  const int gsz = min(GROUP_M, tiles_m2 - first);
+  const int r = tile - g * per_group;
+  int m = first + (r % gsz);
+  nb = r / gsz;
+  if (a.m_order == 1) {
+    const int bpr = a.m_bpr / 2, n = a.comm.nranks, rk = a.comm.rank;
+    if (m < bpr) {
+      m = rk * bpr + m;
+    } else {
+      const int i = m - bpr, j = i / (n - 1), q = i % (n - 1) + 1;
+      m = ((rk + q) % n) * bpr + j;
+    }
+  } else if (a.m_order == 2) {
+    const int bpr = a.m_bpr / 2, n = a.comm.nranks;
+    const int j = m / n, sft = (m % n + a.comm.rank) % n;
+    m = sft * bpr + j;
+  }
+  mb2 = m;
+}
+
+template <int EPI, int COMM>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Args a) {
+  if (COMM != kCommNone && static_cast<int>(blockIdx.x) < a.comm_ctas) {
+    if (COMM == kCommAllGatherPush) comm_allgather_push(a, blockIdx.x, a.comm_ctas);
+    if (COMM == kCommReduceScatter) comm_reduce_scatter(a, blockIdx.x, a.comm_ctas);
+    return;
+  }
+  const int cta_id = (COMM != kCommNone) ? static_cast<int>(blockIdx.x) - a.comm_ctas : static_cast<int>(blockIdx.x);
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + pair::STAGES * pair::STAGE_BYTES);
+  uint64_t* full_bar = bars;                           // [STAGES]  used in the leader
+  uint64_t* empty_bar = bars + pair::STAGES;           // [STAGES]  one per CTA
+  uint64_t* tfull_bar = bars + 2 * pair::STAGES;       // [2]       one per CTA
+  uint64_t* tempty_bar = bars + 2 * pair::STAGES + 2;  // [2]       used in the leader
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * pair::STAGES + 4);
+  volatile uint32_t* bail = tmem_holder + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t crank = ptx::cluster_ctarank();  // 0 = leader
+  const bool leader = crank == 0;
+  const int gemm_ctas = (COMM != kCommNone) ? a.gemm_ctas : gridDim.x;
+  const int pairs = gemm_ctas / 2;
+  const int pair_id = cta_id / 2;
+  const int tiles_m2 = (a.M + 2 * BM - 1) / (2 * BM);
+  const int num_tiles = tiles_m2 * a.tiles_n;
+  const int num_kb = (a.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < pair::STAGES; ++s) {
+      ptx::mbar_init(&full_bar[s], 1);   // the leader's arrive.expect_tx; bytes come from both CTAs
+      ptx::mbar_init(&empty_bar[s], 1);  // one tcgen05.commit from the leader
+    }
+    for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(&tfull_bar[i], 1);
+      ptx::mbar_init(&tempty_bar[i], 8);  // four epilogue warps in each of the two CTAs
+    }
+    *bail = 0;
+    ptx::mbar_fence_init();
+    ptx::prefetch_tmap(&tmA);
+    ptx::prefetch_tmap(&tmB);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc_pair(tmem_holder, TMEM_COLS);
+    ptx::tmem_relinquish_pair();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::cluster_sync();  // both CTAs' barriers and TMEM exist before anybody signals the other
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  // cluster addresses of the leader's and the peer's barriers
+  const uint32_t full0 = ptx::mapa(ptx::smem_u32(&full_bar[0]), 0);
+  const uint32_t tempty0 = ptx::mapa(ptx::smem_u32(&tempty_bar[0]), 0);
+  const uint32_t empty_peer = ptx::mapa(ptx::smem_u32(&empty_bar[0]), 1);
+  const uint32_t tfull_peer = ptx::mapa(ptx::smem_u32(&tfull_bar[0]), 1);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int tile = pair_id; tile < num_tiles && !*bail; tile += pairs) {
+        int mb2, nb;
+        pair_tile_coords(a, tile, tiles_m2, mb2, nb);
+        const int mb = 2 * mb2 + static_cast<int>(crank);  // this CTA's 128-row block
+        if (a.a_ready) {
+          if (!wait_flag_geq(a.a_ready + mb, a.a_ready_target, a.comm.timeout_ns, a.comm.abort_flag)) {
+            if (a.err) atomicCAS(a.err, 0u, 0x41470000u | static_cast<uint32_t>(mb));
+            *bail = 1;
+            break;
+          }
+          ptx::fence_proxy_async();
+        }
+        const int m0 = mb * BM;
+        int brow;
+        if (EPI == kEpiSwiGLU) brow = (leader ? 0 : a.b_half_rows) + nb * (BN / 2);  // gate | up
+        else brow = nb * BN + static_cast<int>(crank) * (BN / 2);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % pair::STAGES;
+          const uint32_t ph = (it / pair::STAGES) & 1;
+          if (!ptx::mbar_wait_bounded(&empty_bar[s], ph ^ 1, bail)) break;
+          uint8_t* sA = smem + s * pair::STAGE_BYTES;
+          uint8_t* sB = sA + pair::A_BYTES;
+          if (leader) ptx::mbar_expect_tx(&full_bar[s], 2 * pair::STAGE_BYTES);
+          const uint32_t fb = full0 + static_cast<uint32_t>(s) * 8;
+          ptx::tma_load_2d_pair(sA, &tmA, fb, kb * BK, m0);
+          ptx::tma_load_2d_pair(sB, &tmB, fb, kb * BK, brow);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader only)
+    if (leader && lane == 0) {
+      constexpr uint32_t idesc = ptx::umma_idesc_f16(1u, 2 * BM, BN);
+      uint32_t it = 0, tcount = 0;
+      for (int tile = pair_id; tile < num_tiles && !*bail; tile += pairs, ++tcount) {
+        const uint32_t acc = tcount & 1, acc_ph = (tcount >> 1) & 1;
+        if (!ptx::mbar_wait_bounded(&tempty_bar[acc], acc_ph ^ 1, bail)) break;
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % pair::STAGES;
+          const uint32_t ph = (it / pair::STAGES) & 1;
+          if (!ptx::mbar_wait_bounded(&full_bar[s], ph, bail)) break;
+          ptx::tc_fence_after();
+          const uint32_t sA = ptx::smem_u32(smem + s * pair::STAGE_BYTES);
+          const uint64_t da = ptx::umma_smem_desc_sw128(sA);
+          const uint64_t db = ptx::umma_smem_desc_sw128(sA + pair::A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t koff = static_cast<uint64_t>((k * UMMA_K * 2) >> 4);
+            ptx::umma_f16_pair(d_tmem, da + koff, db + koff, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          // the stage is free in both CTAs once these MMAs have read it
+          ptx::umma_commit_pair(ptx::smem_u32(&empty_bar[s]));
+          ptx::umma_commit_pair(empty_peer + static_cast<uint32_t>(s) * 8);
+        }
+        ptx::umma_commit_pair(ptx::smem_u32(&tfull_bar[acc]));
+        ptx::umma_commit_pair(tfull_peer + acc * 8);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue warps (both CTAs)
+    const int q = warp & 3;
+    uint32_t tcount = 0;
+    for (int tile = pair_id; tile < num_tiles && !*bail; tile += pairs, ++tcount) {
+      int mb2, nb;
+      pair_tile_coords(a, tile, tiles_m2, mb2, nb);
+      const int mb = 2 * mb2 + static_cast<int>(crank);
+      const uint32_t acc = tcount & 1, acc_ph = (tcount >> 1) & 1;
+      if (!ptx::mbar_wait_bounded(&tfull_bar[acc], acc_ph, bail)) break;
+      ptx::tc_fence_after();
+      const int row = mb * BM + q * 32 + lane;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+      if (EPI == kEpiStore) {
+        __nv_bfloat16* crow = a.C + static_cast<size_t>(row) * a.ldc + static_cast<size_t>(nb) * BN;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          ptx::tmem_ld_32x32b_x32(taddr + c * 32, r);
+          ptx::tmem_ld_wait();
+          const int col0 = nb * BN + c * 32;
+          if (row < a.M) {
+            if (col0 + 32 <= a.N) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint4 v;
+                v.x = ptx::pack_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+                v.y = ptx::pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+                v.z = ptx::pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+                v.w = ptx::pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+                *reinterpret_cast<uint4*>(crow + c * 32 + j * 8) = v;
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < a.N) crow[c * 32 + j] = __float2bfloat16(__uint_as_float(r[j]));
+            }
+          }
+        }
+      } else {
+        const int out_n = a.N / 2;
+        __nv_bfloat16* crow = a.C + static_cast<size_t>(row) * a.ldc + static_cast<size_t>(nb) * (BN / 2);
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          uint32_t g[32], u[32];
+          ptx::tmem_ld_32x32b_x32(taddr + c * 32, g);
+          ptx::tmem_ld_32x32b_x32(taddr + BN / 2 + c * 32, u);
+          ptx::tmem_ld_wait();
+          const int col0 = nb * (BN / 2) + c * 32;
+          if (row < a.M) {
+            if (col0 + 32 <= out_n) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float h[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                  h[e] = silu_f(__uint_as_float(g[8 * j + e])) * __uint_as_float(u[8 * j + e]);
+                uint4 v;
+                v.x = ptx::pack_bf16x2(h[0], h[1]);
+                v.y = ptx::pack_bf16x2(h[2], h[3]);
+                v.z = ptx::pack_bf16x2(h[4], h[5]);
+                v.w = ptx::pack_bf16x2(h[6], h[7]);
+                *reinterpret_cast<uint4*>(crow + c * 32 + j * 8) = v;
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < out_n)
+                  crow[c * 32 + j] = __float2bfloat16(silu_f(__uint_as_float(g[j])) * __uint_as_float(u[j]));
+            }
+          }
+        }
+      }
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive_cluster(tempty0 + acc * 8);
+      if (COMM == kCommReduceScatter) {
+        if (lane == 0) {
+          ptx::fence_sys();
+          const int owner = min((mb * BM) / a.comm.rows_per_rank, a.comm.nranks - 1);
+          ptx::red_release_sys_add_u32(a.comm.done_peer[owner] + mb, 1u);
+        }
+      }
+    }
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::cluster_sync();  // nobody leaves while the other CTA may still signal it or read its memory
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && *bail && a.err) atomicCAS(a.err, 0u, 0x47454d32u);
 }
 
 }  // namespace gemm

@@ -332,19 +332,24 @@ __global__ void __launch_bounds__(kThreads, 1) ring_kernel(const __grid_constant
                          nullptr, len);
     }
   } else {
-    // reduce-scatter: the partial sum of a chunk hops around the ring and gains one term per hop
+    // reduce-scatter: the partial sum of a chunk hops around the ring and gains one term per hop.
+    // Step 0 only sends, steps 1..n-2 receive + add + forward, step n-1 receives + adds into the
+    // output.  The slice is cut into rounds of one piece per chunk, so that the send-only first
+    // step never needs more than one free slot and the pieces travel in the order the successor
+    // consumes them.
     size_t so, sl;
     split(a.count, B, b, &so, &sl);
     const size_t chunkStride = a.count * V::ES, off = so * V::ES, len = sl * V::ES;
-    for (int s = 0; s < n - 1 && ok; ++s) {
-      const int sc = a.ringRanks[((pos - s - 1) % n + n) % n], rc = a.ringRanks[((pos - s - 2) % n + n) % n];
-      const bool last = s == n - 2;
-      if (s == 0) {
-        // first hop: send my term of chunk sc; what arrives is combined below
-        ok = ring_step<DT>(ch, in + sc * chunkStride + off, len, last ? RECV_SUM : RECV_SUM_SEND, out + off,
-                           in + rc * chunkStride + off, len);
-      } else {
-        ok = ring_step<DT>(ch, nullptr, 0, last ? RECV_SUM : RECV_SUM_SEND, out + off, in + rc * chunkStride + off, len);
+    const size_t piece = ch.slotBytes;
+    for (size_t ro = 0; ro < len && ok; ro += piece) {
+      const size_t nb = min(piece, len - ro);
+      const int c0 = a.ringRanks[((pos - 1) % n + n) % n];
+      ok = ring_step<DT>(ch, in + c0 * chunkStride + off + ro, nb, RECV_NONE, nullptr, nullptr, 0);
+      for (int k = 1; k < n && ok; ++k) {
+        const int rc = a.ringRanks[((pos - 1 - k) % n + n) % n];
+        const bool last = k == n - 1;
+        ok = ring_step<DT>(ch, nullptr, 0, last ? RECV_SUM : RECV_SUM_SEND, out + off + ro,
+                           in + rc * chunkStride + off + ro, nb);
       }
     }
   }

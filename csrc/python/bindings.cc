@@ -220,6 +220,8 @@ PYBIND11_MODULE(_uccl_bindings, m) {
     check(ucclCommSetAlgo(C(c), static_cast<ucclAlgo_t>(algo), static_cast<ucclProto_t>(proto)), "ucclCommSetAlgo");
   });
 
+  m.def("set_blocks", [](uintptr_t c, int blocks) { check(ucclCommSetBlocks(C(c), blocks), "ucclCommSetBlocks"); });
+
   // ---------------------------------------------------------------- local ops
   m.def("gemm_bf16",
         [](uintptr_t A, uintptr_t B, uintptr_t Cp, int M, int N, int K, int lda, int ldb, int ldc, int epilogue,

@@ -273,6 +273,8 @@ ucclResult_t ucclCommQueryTuning(ucclComm_t comm, ucclCollKind_t coll, size_t by
 ucclResult_t ucclCommLoadTuning(ucclComm_t comm, const char* jsonPath);
 /* Force algorithm/protocol for subsequent calls on this communicator (Auto = tuner). */
 ucclResult_t ucclCommSetAlgo(ucclComm_t comm, ucclAlgo_t algo, ucclProto_t proto);
+/* Force the number of CTAs ("channels") of subsequent collective kernels; 0 returns to the tuner. */
+ucclResult_t ucclCommSetBlocks(ucclComm_t comm, int blocks);
 
 #ifdef __cplusplus
 }

@@ -265,6 +265,10 @@ class Communicator:
     def set_algo(self, algo: str = "auto", proto: str = "auto"):
         _C.set_algo(self._comm, ALGOS[algo], PROTOS[proto])
 
+    def set_blocks(self, blocks: int = 0):
+        """Force the CTA count of collective kernels (0 = let the tuner decide)."""
+        _C.set_blocks(self._comm, int(blocks))
+
     def load_tuning(self, path: str):
         _C.load_tuning(self._comm, path)
 
