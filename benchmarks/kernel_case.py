@@ -5,6 +5,7 @@
     python benchmarks/kernel_case.py --case gemm_swiglu --m 4096 --n 7168 --k 4096
     python benchmarks/kernel_case.py --case add_norm --tokens 8192 --hidden 8192
     python benchmarks/kernel_case.py --case moe_dispatch --tokens 4096 --hidden 7168
+    python benchmarks/kernel_case.py --case gemm_rs_self --m 8192 --n 4096 --k 1792
 
 Prints one JSON line with the median device time and the achieved fraction of the measured
 peaks in MEASURED_PEAKS.json (copy bandwidth for the memory-bound cases, cuBLAS bf16 burst
@@ -88,6 +89,33 @@ def main():
         out.update(tokens=args.tokens, hidden=args.hidden, topk=args.topk, ms=round(t["median"], 4),
                    gbs=round(nbytes / t["median"] / 1e6, 1), frac_of_copy_bw=round(nbytes / t["median"] / 1e6 / peaks["hbm_gbs"], 3))
         disp.close()
+        comm.destroy()
+    elif args.case in ("gemm_rs_self", "ag_gemm_self"):
+        # the fused tensor-parallel kernels on a one-rank communicator: tiles are staged and
+        # summed (reduce-scatter) or flagged (all-gather) exactly as with peers, all on this GPU
+        os.environ["UCCL_FUSED_SELF"] = "1"
+        from unified_ccl_b200 import Communicator
+        from unified_ccl_b200.parallel import allgather_gemm, gemm_reduce_scatter
+
+        comm = Communicator(0, 1)
+        a = torch.randn(args.m, args.k, device=dev).to(torch.bfloat16)
+        b = (torch.randn(args.n, args.k, device=dev) * 0.02).to(torch.bfloat16)
+        if args.case == "gemm_rs_self":
+            stage = comm.empty((args.m, args.n), torch.bfloat16)
+            y = torch.empty(args.m, args.n, device=dev, dtype=torch.bfloat16)
+            fn = lambda: gemm_reduce_scatter(comm, a, b, stage, out=y)  # noqa: E731
+        else:
+            full = comm.empty((args.m, args.k), torch.bfloat16)
+            y = torch.empty(args.m, args.n, device=dev, dtype=torch.bfloat16)
+            fn = lambda: allgather_gemm(comm, a, full, b, out=y)  # noqa: E731
+        fn()
+        torch.cuda.synchronize()
+        ref = a.float() @ b.float().t()
+        err = float((y.float() - ref).abs().max() / ref.abs().max())
+        t = device_time_ms(fn, args.iters, args.warmup)
+        flops = 2.0 * args.m * args.n * args.k
+        out.update(m=args.m, n=args.n, k=args.k, ms=round(t["median"], 4), tflops=round(flops / t["median"] / 1e9, 1),
+                   max_rel_err=round(err, 5), debug=os.environ.get("UCCL_FUSED_DEBUG", "0"))
         comm.destroy()
     else:
         raise SystemExit("unknown case " + args.case)

@@ -96,6 +96,7 @@ struct Comm {
   cudaEvent_t ceEvent[UCCL_MAX_LOCAL_RANKS] = {};
   cudaEvent_t ceStart = nullptr;
   bool ceReady = false;
+  void* onesDev = nullptr;            // 32-bit ones at the GEMM flag stride (source of copy-engine flag writes)
 
   // network path
   ucclNet_t* net = nullptr;

@@ -19,6 +19,7 @@
 #include "../kernels/coll_device_types.h"
 #include "../kernels/collectives.cuh"
 #include "log.h"
+#include "trace.h"
 
 namespace uccl {
 
@@ -470,8 +471,10 @@ ucclResult_t executeOp(const CollOp& op) {
     return localCopy(c, op.send, op.recv, op.count * es, op.stream);
   }
 
+  TraceScope trace(c, collName(op.kind), msgBytes, op.stream);
   if (c->useNet || !c->p2pReady) {
     commCount(c, op.kind, msgBytes, ucclAlgoNet);
+    trace.setAlgo(ucclAlgoNet);
     return enqueueNetGpu(c, op);
   }
 
@@ -484,6 +487,7 @@ ucclResult_t executeOp(const CollOp& op) {
   }
   TuneChoice ch = chooseFor(c, op.kind, msgBytes, sym, nvls, op.dtype);
   commCount(c, op.kind, msgBytes, ch.algo);
+  trace.setAlgo(ch.algo);
   UCCL_LOG(TRACE, "%s bytes=%zu algo=%s proto=%s blocks=%d sym=%d", collName(op.kind), msgBytes, algoName(ch.algo),
            protoName(ch.proto), ch.blocks, (int)sym);
 

@@ -41,6 +41,13 @@ ucclResult_t enqueueRing(Comm* c, const CollOp& op, ucclProto_t proto, int block
 ucclResult_t enqueueCopyEngine(Comm* c, const CollOp& op);
 // A stream-ordered barrier among the ranks of the NVLink domain (one tiny kernel).
 ucclResult_t enqueueBarrier(Comm* c, cudaStream_t s);
+// device-to-device copy on a side stream, concurrent with what follows on `s` until sideCopyEnd
+ucclResult_t sideCopyBegin(Comm* c, void* dst, const void* src, size_t bytes, cudaStream_t s);
+ucclResult_t sideCopyEnd(Comm* c, cudaStream_t s);
+// copy-engine all-gather with per-row-block arrival flags (all-gather -> GEMM fusion)
+ucclResult_t allGatherPushBegin(Comm* c, const void* shard, char* const* fullPeer, char* const* readyPeer,
+                                size_t shardBytes, int blocksPerRank, bool copyOwn, cudaStream_t s);
+ucclResult_t allGatherPushEnd(Comm* c, bool copyOwn, cudaStream_t s);
 ucclResult_t enqueueNetGpu(Comm* c, const CollOp& op);
 ucclResult_t enqueueNetGpuP2p(Comm* c, const std::vector<CollOp>& ops);
 

@@ -13,6 +13,8 @@
 // copy_engine.cc:88-97).
 #include <string.h>
 
+#include <stdlib.h>
+
 #include <algorithm>
 
 #include "../kernels/coll_device_types.h"
@@ -61,6 +63,86 @@ ucclResult_t joinStreams(Comm* c, cudaStream_t s) {
   }
   return ucclSuccess;
 }
+
+}  // namespace
+
+// A device-to-device copy that runs on a side stream next to whatever follows on `s`:
+// sideCopyBegin forks after the work already enqueued on `s`, sideCopyEnd makes `s` wait for it.
+ucclResult_t sideCopyBegin(Comm* c, void* dst, const void* src, size_t bytes, cudaStream_t s) {
+  const ucclResult_t r = ensureCeStreams(c);
+  if (r != ucclSuccess) return r;
+  if (cudaEventRecord(c->ceStart, s) != cudaSuccess) return cudaFail(c, "cudaEventRecord");
+  if (cudaStreamWaitEvent(c->ceStream[0], c->ceStart, 0) != cudaSuccess) return cudaFail(c, "cudaStreamWaitEvent");
+  if (cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, c->ceStream[0]) != cudaSuccess)
+    return cudaFail(c, "cudaMemcpyAsync");
+  return ucclSuccess;
+}
+// All-gather by copy engines for the all-gather -> GEMM fusion: this rank's shard goes to rows
+// [rank * rows, ...) of every rank's A buffer in `chunks` pieces per peer, each followed (in stream
+// order, on the same side stream) by a strided copy of ones onto the peer's arrival flags of the
+// row blocks it covers.  The GEMM kernel launched on `s` meanwhile polls those flags.  Call
+// allGatherPushEnd after the kernel launch.
+ucclResult_t allGatherPushBegin(Comm* c, const void* shard, char* const* fullPeer, char* const* readyPeer,
+                                size_t shardBytes, int blocksPerRank, bool copyOwn, cudaStream_t s) {
+  const ucclResult_t r = ensureCeStreams(c);
+  if (r != ucclSuccess) return r;
+  const int n = c->localRanks, me = c->localRank;
+  if (!c->onesDev) {
+    // a column of 32-bit ones at the flag stride, the source of every flag copy
+    if (cudaMalloc(&c->onesDev, kGemmFlagStrideBytes * kGemmMaxRowBlocks) != cudaSuccess) return cudaFail(c, "cudaMalloc");
+    if (cudaMemset(c->onesDev, 0, kGemmFlagStrideBytes * kGemmMaxRowBlocks) != cudaSuccess ||
+        cudaMemset2D(c->onesDev, kGemmFlagStrideBytes, 1, 1, kGemmMaxRowBlocks) != cudaSuccess)
+      return cudaFail(c, "cudaMemset2D");
+  }
+  if (cudaEventRecord(c->ceStart, s) != cudaSuccess) return cudaFail(c, "cudaEventRecord");
+  for (int p = 0; p < n; ++p) {
+    if (p == me && !copyOwn) continue;
+    if (cudaStreamWaitEvent(c->ceStream[p], c->ceStart, 0) != cudaSuccess) return cudaFail(c, "cudaStreamWaitEvent");
+  }
+  const size_t blkBytes = shardBytes / blocksPerRank;
+  int wantChunks = c->cfg.fusedCeChunks > 0 ? c->cfg.fusedCeChunks : 4;
+  if (const char* e = getenv("UCCL_FUSED_CE_CHUNKS")) {  // read per call so that a tuning run can vary it
+    if (atoi(e) > 0) wantChunks = atoi(e);
+  }
+  const int chunks = std::min(wantChunks, blocksPerRank);
+  const char* src = static_cast<const char*>(shard);
+  const size_t rowOff = static_cast<size_t>(me) * shardBytes;
+  for (int j = 0; j < chunks; ++j) {
+    const int b0 = static_cast<int>(static_cast<long long>(blocksPerRank) * j / chunks);
+    const int b1 = static_cast<int>(static_cast<long long>(blocksPerRank) * (j + 1) / chunks);
+    if (b1 == b0) continue;
+    const size_t off = b0 * blkBytes, len = (b1 - b0) * blkBytes;
+    for (int q = 1; q < n; ++q) {
+      const int p = (me + q) % n;
+      if (cudaMemcpyAsync(fullPeer[p] + rowOff + off, src + off, len, cudaMemcpyDeviceToDevice, c->ceStream[p]) != cudaSuccess)
+        return cudaFail(c, "cudaMemcpyAsync");
+      if (cudaMemcpy2DAsync(readyPeer[p] + (static_cast<size_t>(me) * blocksPerRank + b0) * kGemmFlagStrideBytes,
+                            kGemmFlagStrideBytes, c->onesDev, kGemmFlagStrideBytes, sizeof(uint32_t), b1 - b0,
+                            cudaMemcpyDeviceToDevice, c->ceStream[p]) != cudaSuccess)
+        return cudaFail(c, "cudaMemcpy2DAsync");
+    }
+  }
+  if (copyOwn &&
+      cudaMemcpyAsync(fullPeer[me] + rowOff, src, shardBytes, cudaMemcpyDeviceToDevice, c->ceStream[me]) != cudaSuccess)
+    return cudaFail(c, "cudaMemcpyAsync");
+  return ucclSuccess;
+}
+ucclResult_t allGatherPushEnd(Comm* c, bool copyOwn, cudaStream_t s) {
+  for (int p = 0; p < c->localRanks; ++p) {
+    if (p == c->localRank && !copyOwn) continue;
+    if (cudaEventRecord(c->ceEvent[p], c->ceStream[p]) != cudaSuccess) return cudaFail(c, "cudaEventRecord");
+    if (cudaStreamWaitEvent(s, c->ceEvent[p], 0) != cudaSuccess) return cudaFail(c, "cudaStreamWaitEvent");
+  }
+  return ucclSuccess;
+}
+
+ucclResult_t sideCopyEnd(Comm* c, cudaStream_t s) {
+  if (cudaEventRecord(c->ceEvent[0], c->ceStream[0]) != cudaSuccess) return cudaFail(c, "cudaEventRecord");
+  if (cudaStreamWaitEvent(s, c->ceEvent[0], 0) != cudaSuccess) return cudaFail(c, "cudaStreamWaitEvent");
+  return ucclSuccess;
+}
+
+namespace {
 
 ucclResult_t localReduce(Comm* c, char* dst, const char* slots, int nslots, size_t slotStride, size_t bytes,
                          ucclDataType_t dt, cudaStream_t s) {

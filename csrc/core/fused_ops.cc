@@ -5,6 +5,7 @@
 // row-parallel down projection ends in a reduce-scatter).
 #include <stdlib.h>
 #include <string.h>
+#include <strings.h>
 
 #include <algorithm>
 
@@ -52,6 +53,23 @@ int fusedCommCtas(Comm* c) {
     if (v >= 1 && v <= 64) return v;
   }
   return c->cfg.maxCtas > 0 ? std::min(c->cfg.maxCtas, 32) : 8;
+}
+
+// How the all-gather of the all-gather -> GEMM fusion moves its rows: copy engines next to the
+// GEMM (default: no SM is taken from the GEMM and the links run at full rate) or communication
+// CTAs inside the launch (UCCL_FUSED_AG=kernel, or an SM algorithm forced on the communicator).
+bool fusedAgByCopyEngine(Comm* c) {
+  const char* s = getenv("UCCL_FUSED_AG");
+  if (s && *s) return !strcasecmp(s, "ce") || !strcasecmp(s, "copy_engine");
+  if (c->forcedAlgo == ucclAlgoOneShot || c->forcedAlgo == ucclAlgoTwoShot || c->forcedAlgo == ucclAlgoRing) return false;
+  return true;
+}
+
+// UCCL_FUSED_SELF=1 runs the fused kernels on a one-rank communicator too (every "peer" is this
+// GPU): the whole data path of the fusion in a single process, for profiling one kernel alone.
+bool fusedSelf() {
+  const char* s = getenv("UCCL_FUSED_SELF");
+  return s && atoi(s) != 0;
 }
 
 struct Sym {
@@ -164,7 +182,7 @@ extern "C" ucclResult_t ucclAllGatherGemm(const void* xShard, void* xFull, const
   g.ldc = epilogue == 1 ? N / 2 : N;
   g.epilogue = epilogue;
   g.err = c->hostFlagsDev + 16;
-  if (c->nRanks == 1) {
+  if (c->nRanks == 1 && !fusedSelf()) {
     g.A = xShard;
     return launchGemmBf16(g, nullptr, s);
   }
@@ -172,34 +190,57 @@ extern "C" ucclResult_t ucclAllGatherGemm(const void* xShard, void* xFull, const
     commSetError(c, "all-gather GEMM needs M / nranks to be a multiple of 128 (M=%d, nranks=%d)", M, n);
     return ucclInvalidArgument;
   }
-  if (M / 128 > 4096) return ucclInvalidArgument;
+  if (M / 128 > kGemmMaxRowBlocks) return ucclInvalidArgument;
   Sym sf;
   if (!symOf(c, xFull, static_cast<size_t>(M) * K * 2, &sf)) {
     commSetError(c, "xFull must come from ucclMemAlloc");
     return ucclInvalidArgument;
   }
-  // arrival flags start at zero; nobody pushes before every rank has cleared its own
+  const int rows = M / n;
+  const size_t shardBytes = static_cast<size_t>(rows) * K * 2;
+  const char* myRows = static_cast<const char*>(xFull) + static_cast<size_t>(c->localRank) * shardBytes;
+  if (reinterpret_cast<uintptr_t>(xShard) & 15) return ucclInvalidArgument;
+  // Arrival counters start at zero.  The barrier orders the zeroing before any rank's pushes, and
+  // those pushes after every rank's previous readers of its xFull.
   uint32_t* ready = reinterpret_cast<uint32_t*>(c->arena->local + kArenaGemmReadyOff);
-  if (cudaMemsetAsync(ready, 0, sizeof(uint32_t) * (M / 128), s) != cudaSuccess) return ucclSystemError;
+  if (cudaMemsetAsync(ready, 0, kGemmFlagStrideBytes * (M / 128), s) != cudaSuccess) return ucclSystemError;
   if ((r = enqueueBarrier(c, s)) != ucclSuccess) return r;
   GemmFusion f;
   f.role = 1;
   f.rank = c->localRank;
   f.nranks = n;
   f.comm_ctas = fusedCommCtas(c);
-  f.epoch = 1;
   f.timeout_ns = c->dev.timeoutNs;
   f.abort_flag = c->dev.abortFlag;
-  f.rows_per_rank = M / n;
-  f.a_local = xShard;
-  f.use_multimem = (sf.seg->mc && c->forcedAlgo != ucclAlgoTwoShot) ? 1 : 0;
-  f.a_full_mc = sf.seg->mc ? sf.seg->mc + sf.off : nullptr;
+  f.rows_per_rank = rows;
+  f.a_shard = xShard;
+  f.a_inplace = myRows == static_cast<const char*>(xShard) ? 1 : 0;
   for (int p = 0; p < n; ++p) {
     f.a_full_peer[p] = sf.seg->peer[p] + sf.off;
     f.ready_peer[p] = reinterpret_cast<uint32_t*>(c->arena->peer[p] + kArenaGemmReadyOff);
   }
-  commCount(c, ucclCollAllGather, static_cast<size_t>(M) * K * 2, f.use_multimem ? ucclAlgoNvls : ucclAlgoTwoShot);
-  return launchGemmBf16(g, &f, s);
+  // Two ways to move the rows: communication CTAs inside the GEMM launch (default), or copy
+  // engines on side streams next to it (UCCL_FUSED_AG=ce, or algorithm copy_engine forced).
+  if (fusedAgByCopyEngine(c)) {
+    commCount(c, ucclCollAllGather, static_cast<size_t>(M) * K * 2, ucclAlgoCopyEngine);
+    f.a_external = 1;
+    char* fullPeer[UCCL_MAX_LOCAL_RANKS];
+    char* readyPeer[UCCL_MAX_LOCAL_RANKS];
+    for (int p = 0; p < n; ++p) {
+      fullPeer[p] = static_cast<char*>(f.a_full_peer[p]);
+      readyPeer[p] = reinterpret_cast<char*>(f.ready_peer[p]);
+    }
+    if ((r = allGatherPushBegin(c, xShard, fullPeer, readyPeer, shardBytes, rows / 128, !f.a_inplace, s)) != ucclSuccess)
+      return r;
+    if ((r = launchGemmBf16(g, &f, s)) != ucclSuccess) return r;
+    return allGatherPushEnd(c, !f.a_inplace, s);
+  }
+  commCount(c, ucclCollAllGather, static_cast<size_t>(M) * K * 2, ucclAlgoOneShot);
+  // The kernel reads my rows from the shard; a copy engine puts them into xFull meanwhile.
+  if (!f.a_inplace && (r = sideCopyBegin(c, const_cast<char*>(myRows), xShard, shardBytes, s)) != ucclSuccess) return r;
+  if ((r = launchGemmBf16(g, &f, s)) != ucclSuccess) return r;
+  if (!f.a_inplace) return sideCopyEnd(c, s);
+  return ucclSuccess;
 }
 
 extern "C" ucclResult_t ucclGemmReduceScatter(const void* A, const void* W, void* cPartial, void* out, int M, int N,
@@ -222,7 +263,7 @@ extern "C" ucclResult_t ucclGemmReduceScatter(const void* A, const void* W, void
   g.ldb = K;
   g.ldc = N;
   g.err = c->hostFlagsDev + 16;
-  if (c->nRanks == 1) {
+  if (c->nRanks == 1 && !fusedSelf()) {
     g.C = out;
     return launchGemmBf16(g, nullptr, s);
   }
@@ -230,34 +271,33 @@ extern "C" ucclResult_t ucclGemmReduceScatter(const void* A, const void* W, void
     commSetError(c, "GEMM reduce-scatter needs M / nranks to be a multiple of 128 and N a multiple of 8");
     return ucclInvalidArgument;
   }
-  if (M / 128 > 4096) return ucclInvalidArgument;
+  if (M / 128 > kGemmMaxRowBlocks) return ucclInvalidArgument;
   Sym sp;
   if (!symOf(c, cPartial, static_cast<size_t>(M) * N * 2, &sp)) {
     commSetError(c, "cPartial must come from ucclMemAlloc");
     return ucclInvalidArgument;
   }
+  // cPartial is the staging buffer of this rank: slot s ([rows_per_rank, N]) receives rank s's
+  // partial sums of this rank's rows.  The counters start at zero, and the barrier also orders
+  // this launch's remote writes after every rank's previous use of its staging buffer.
   uint32_t* done = reinterpret_cast<uint32_t*>(c->arena->local + kArenaGemmDoneOff);
-  if (cudaMemsetAsync(done, 0, sizeof(uint32_t) * (M / 128), s) != cudaSuccess) return ucclSystemError;
+  if (cudaMemsetAsync(done, 0, kGemmFlagStrideBytes * (M / 128), s) != cudaSuccess) return ucclSystemError;
   if ((r = enqueueBarrier(c, s)) != ucclSuccess) return r;
   GemmFusion f;
   f.role = 2;
   f.rank = c->localRank;
   f.nranks = n;
-  f.comm_ctas = fusedCommCtas(c);
-  f.epoch = 1;
   f.timeout_ns = c->dev.timeoutNs;
   f.abort_flag = c->dev.abortFlag;
   f.rows_per_rank = M / n;
-  f.use_multimem = (sp.seg->mc && c->forcedAlgo != ucclAlgoTwoShot) ? 1 : 0;
-  f.c_part_mc = sp.seg->mc ? sp.seg->mc + sp.off : nullptr;
   for (int p = 0; p < n; ++p) {
-    f.c_part_peer[p] = sp.seg->peer[p] + sp.off;
+    f.stage_peer[p] = sp.seg->peer[p] + sp.off;
     f.done_peer[p] = reinterpret_cast<uint32_t*>(c->arena->peer[p] + kArenaGemmDoneOff);
   }
   f.rs_out = out;
   f.rs_ldo = N;
-  commCount(c, ucclCollReduceScatter, static_cast<size_t>(M) * N * 2, f.use_multimem ? ucclAlgoNvls : ucclAlgoTwoShot);
-  if ((r = launchGemmBf16(g, &f, s)) != ucclSuccess) return r;
-  // peers may still be reading this rank's partial tiles: nobody reuses cPartial before all are done
-  return enqueueBarrier(c, s);
+  commCount(c, ucclCollReduceScatter, static_cast<size_t>(M) * N * 2, ucclAlgoOneShot);
+  // When the kernel ends, every partial tile for this rank has arrived and been summed, and this
+  // rank's own stores to its peers are complete: nothing is in flight in either direction.
+  return launchGemmBf16(g, &f, s);
 }

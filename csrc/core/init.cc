@@ -18,6 +18,7 @@
 #include "../transport/net_plugin.h"
 #include "cuda_driver.h"
 #include "log.h"
+#include "trace.h"
 
 namespace uccl {
 
@@ -91,6 +92,27 @@ ucclResult_t commPollDeviceStatus(Comm* c) {
   __atomic_store_n(&c->hostFlags[0], 1u, __ATOMIC_RELEASE);
   __atomic_store_n(&c->hostFlags[8], 0u, __ATOMIC_RELEASE);
   return ucclRemoteError;
+}
+
+void traceDump(Comm* c) {
+  if (c->trace.empty()) return;
+  FILE* f = nullptr;
+  if (!c->cfg.traceFile.empty()) {
+    char path[600];
+    snprintf(path, sizeof(path), "%s.%d", c->cfg.traceFile.c_str(), c->rank);
+    f = fopen(path, "w");
+  }
+  for (TraceEvent& t : c->trace) {
+    float ms = 0.f;
+    if (f && t.start && t.stop && cudaEventElapsedTime(&ms, t.start, t.stop) == cudaSuccess)
+      fprintf(f, "{\"op\": \"%s\", \"bytes\": %zu, \"algo\": \"%s\", \"us\": %.2f}\n", t.name, t.bytes,
+              algoName(static_cast<ucclAlgo_t>(t.algo)), ms * 1e3f);
+    if (t.start) cudaEventDestroy(t.start);
+    if (t.stop) cudaEventDestroy(t.stop);
+  }
+  (void)cudaGetLastError();
+  if (f) fclose(f);
+  c->trace.clear();
 }
 
 namespace {
@@ -343,12 +365,10 @@ void destroyComm(Comm* c) {
       if (c->ceEvent[i]) cudaEventDestroy(c->ceEvent[i]);
     }
     if (c->ceStart) cudaEventDestroy(c->ceStart);
+    if (c->onesDev) cudaFree(c->onesDev);
     if (c->epochsDev) cudaFree(c->epochsDev);
     if (c->hostFlags) cudaFreeHost(c->hostFlags);
-    for (TraceEvent& t : c->trace) {
-      cudaEventDestroy(t.start);
-      cudaEventDestroy(t.stop);
-    }
+    traceDump(c);
   }
   c->bootstrap.close();
   c->magic = 0;

@@ -38,11 +38,19 @@ __device__ __forceinline__ bool aborted(const DevComm& dc) {
 // Spins until (int)(*p - target) >= 0.  Gives up on abort or after dc.timeoutNs.
 __device__ __forceinline__ bool wait_u32(const uint32_t* p, uint32_t target, const DevComm& dc, uint32_t code,
                                          int peer, uint32_t step) {
-  if (static_cast<int32_t>(ptx::ld_acquire_sys_u32(p) - target) >= 0) return true;
+  // poll with relaxed loads and order the data behind the flag with one fence on success: an
+  // acquire on every poll is a system-scope fence per iteration
+  if (static_cast<int32_t>(ptx::ld_relaxed_sys_u32(p) - target) >= 0) {
+    ptx::fence_sys();
+    return true;
+  }
   const uint64_t t0 = ptx::globaltimer_ns();
   uint32_t spins = 0;
   while (true) {
-    if (static_cast<int32_t>(ptx::ld_acquire_sys_u32(p) - target) >= 0) return true;
+    if (static_cast<int32_t>(ptx::ld_relaxed_sys_u32(p) - target) >= 0) {
+      ptx::fence_sys();
+      return true;
+    }
     if ((++spins & 31u) == 0) {
       if (aborted(dc)) return false;
       if (ptx::globaltimer_ns() - t0 > dc.timeoutNs) {
@@ -54,11 +62,17 @@ __device__ __forceinline__ bool wait_u32(const uint32_t* p, uint32_t target, con
 }
 __device__ __forceinline__ bool wait_u64(const uint64_t* p, uint64_t target, const DevComm& dc, uint32_t code,
                                          int peer, uint32_t step) {
-  if (ptx::ld_acquire_sys_u64(p) >= target) return true;
+  if (ptx::ld_relaxed_sys_u64(p) >= target) {
+    ptx::fence_sys();
+    return true;
+  }
   const uint64_t t0 = ptx::globaltimer_ns();
   uint32_t spins = 0;
   while (true) {
-    if (ptx::ld_acquire_sys_u64(p) >= target) return true;
+    if (ptx::ld_relaxed_sys_u64(p) >= target) {
+      ptx::fence_sys();
+      return true;
+    }
     if ((++spins & 31u) == 0) {
       if (aborted(dc)) return false;
       if (ptx::globaltimer_ns() - t0 > dc.timeoutNs) {

@@ -22,22 +22,22 @@ struct GemmLaunch {
 
 // Fusion descriptor filled by the tensor-parallel entry points.
 struct GemmFusion {
-  int role = 0;  // 0 none, 1 all-gather push, 2 reduce-scatter
+  int role = 0;  // 0 none, 1 all-gather (push), 2 reduce-scatter (push + local sum)
   int rank = 0, nranks = 1;
-  int comm_ctas = 0;
-  int use_multimem = 0;
-  uint32_t epoch = 1;
+  int comm_ctas = 0;         // all-gather: CTAs that move data (reduce-scatter reserves none)
   uint64_t timeout_ns = 0;
   uint32_t* abort_flag = nullptr;
   int rows_per_rank = 0;
-  // all-gather
-  const void* a_local = nullptr;
+  // all-gather: my shard, every rank's A_full (peer-mapped) and every rank's arrival counters
+  // (zeroed before the launch); a_inplace: the shard already sits in my A_full
+  const void* a_shard = nullptr;
+  int a_inplace = 0;
+  int a_external = 0;  // the rows arrive by copy engines: no communication CTAs, flags are set to 1
   void* a_full_peer[UCCL_MAX_LOCAL_RANKS] = {};
-  void* a_full_mc = nullptr;
   uint32_t* ready_peer[UCCL_MAX_LOCAL_RANKS] = {};
-  // reduce-scatter
-  const void* c_part_peer[UCCL_MAX_LOCAL_RANKS] = {};
-  const void* c_part_mc = nullptr;
+  // reduce-scatter: every rank's staging buffer [nranks][rows_per_rank][N] (peer-mapped) and
+  // per-row-block counters (zeroed before the launch); output of this rank
+  void* stage_peer[UCCL_MAX_LOCAL_RANKS] = {};
   uint32_t* done_peer[UCCL_MAX_LOCAL_RANKS] = {};
   void* rs_out = nullptr;
   int rs_ldo = 0;

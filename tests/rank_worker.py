@@ -286,22 +286,29 @@ def case_tp_mlp(comm, rank, n, args):
 
     dev = _dev(comm, rank)
     fail = []
-    for hidden, ffn, tokens in ((512, 1024, 256 * n), (1024, 3584 * 2, 128 * n)):
-        mlp = TensorParallelMLP(comm, hidden, ffn, tokens, seed=3)
-        x_full = torch.randn(tokens, hidden, generator=torch.Generator().manual_seed(11)).to(torch.bfloat16).to(dev)
-        rows = tokens // n
-        x_shard = x_full[rank * rows:(rank + 1) * rows].contiguous()
-        for it in range(3):  # repeated calls reuse flags and scratch buffers
-            y = mlp(x_shard)
-        _sync(comm)
-        part = mlp.reference(x_full).contiguous()
-        comm.allreduce(part)
-        _sync(comm)
-        ref = part[rank * rows:(rank + 1) * rows]
-        err = (y.float() - ref).abs().max().item()
-        scale = ref.abs().max().item()
-        if not err <= 3e-2 * scale + 1e-3:
-            fail.append((hidden, ffn, tokens, err, scale))
+    # both ways of moving the all-gather's rows: copy engines next to the GEMM, and CTAs inside it
+    for ag_mode in ("ce", "kernel"):
+        os.environ["UCCL_FUSED_AG"] = ag_mode
+        for hidden, ffn, tokens in ((512, 1024, 256 * n), (1024, 3584 * 2, 128 * n)):
+            mlp = TensorParallelMLP(comm, hidden, ffn, tokens, seed=3)
+            x_full = torch.randn(tokens, hidden, generator=torch.Generator().manual_seed(11)).to(torch.bfloat16).to(dev)
+            rows = tokens // n
+            x_shard = x_full[rank * rows:(rank + 1) * rows].contiguous()
+            for it in range(3):  # repeated calls reuse flags and scratch buffers
+                y = mlp(x_shard)
+            _sync(comm)
+            gathered = mlp.x_full.clone()
+            part = mlp.reference(x_full).contiguous()
+            comm.allreduce(part)
+            _sync(comm)
+            ref = part[rank * rows:(rank + 1) * rows]
+            err = (y.float() - ref).abs().max().item()
+            scale = ref.abs().max().item()
+            if not err <= 3e-2 * scale + 1e-3:
+                fail.append((ag_mode, hidden, ffn, tokens, err, scale))
+            if not torch.equal(gathered, x_full):
+                fail.append((ag_mode, "x_full not gathered", hidden, tokens))
+    os.environ.pop("UCCL_FUSED_AG", None)
     return {"fail": fail, "nvls": comm.info["nvls"], "async": comm.async_error(), "last": comm.last_error()}
 
 
