@@ -71,9 +71,14 @@ def main():
     rows = tokens // world
     mlp = TensorParallelMLP(comm, HIDDEN, FFN, tokens, seed=0)
     base = NcclCublasMLP(mlp.w_gate_up, mlp.w_down, tokens, world)
+    autotune = {}
     g = torch.Generator(device="cpu").manual_seed(1234 + rank)
     x_host = torch.randn(rows, HIDDEN, generator=g).to(torch.bfloat16).pin_memory()
     x_dev = x_host.to(dev)
+    # untimed: pick how the all-gather -> GEMM moves its rows on this box (measured, same on every rank)
+    if world > 1 and not os.environ.get("UCCL_FUSED_AG"):
+        autotune = {"%s/ctas%d/chunks%d" % k: v for k, v in mlp.autotune(x_dev).items()}
+        autotune["chosen"] = "%s/ctas%d/chunks%d" % mlp.ag_choice
 
     def barrier():
         if world > 1:
@@ -183,6 +188,7 @@ def main():
             "gpu_launches": launches_per_step * args.steps,
             "allreduce_vs_nccl": sweep,
             "comm": {k: comm.info[k] for k in ("nvls", "p2p_mode", "net_active")},
+            "ag_gemm_autotune_us": autotune,
         }
         print(json.dumps(out))
     barrier()

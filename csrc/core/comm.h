@@ -81,6 +81,7 @@ struct Comm {
   Tuner tuner;
   ucclAlgo_t forcedAlgo = ucclAlgoAuto;
   ucclProto_t forcedProto = ucclProtoAuto;
+  int fusedAgMode = 0, fusedCommCtas = 0, fusedCeChunks = 0;  // ucclCommSetFusedOptions (0 = default)
   int forcedBlocks = 0;               // CTA count forced by ucclCommSetBlocks (0 = tuner)
 
   // NVLink domain

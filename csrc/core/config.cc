@@ -109,8 +109,8 @@ Config loadConfig() {
   if ((s = getenv("UCCL_TRACE_FILE")) && *s) c.traceFile = s;
   c.netChunkBytes = parseSize(getenv("UCCL_NET_CHUNK_BYTES"), 512u << 10);
   if (c.netChunkBytes < 4096) c.netChunkBytes = 4096;
-  c.fusedCeChunks = (int)envLong("UCCL_FUSED_CE_CHUNKS", 4);
-  if (c.fusedCeChunks < 1) c.fusedCeChunks = 1;
+  c.fusedCeChunks = (int)envLong("UCCL_FUSED_CE_CHUNKS", 0);
+  if (c.fusedCeChunks < 0) c.fusedCeChunks = 0;
   return c;
 }
 

@@ -35,7 +35,7 @@ struct Config {
   int p2pMode = 0;                       // UCCL_P2P = 0 auto, 1 cudaIpc, 2 vmm
   std::string traceFile;                 // UCCL_TRACE_FILE
   size_t netChunkBytes = 512u << 10;     // UCCL_NET_CHUNK_BYTES (bounce slot size)
-  int fusedCeChunks = 4;                 // UCCL_FUSED_CE_CHUNKS: copies per peer of the copy-engine all-gather
+  int fusedCeChunks = 0;                 // UCCL_FUSED_CE_CHUNKS: copies per peer of the copy-engine all-gather
 };
 
 Config loadConfig();

@@ -100,7 +100,7 @@ ucclResult_t allGatherPushBegin(Comm* c, const void* shard, char* const* fullPee
     if (cudaStreamWaitEvent(c->ceStream[p], c->ceStart, 0) != cudaSuccess) return cudaFail(c, "cudaStreamWaitEvent");
   }
   const size_t blkBytes = shardBytes / blocksPerRank;
-  int wantChunks = c->cfg.fusedCeChunks > 0 ? c->cfg.fusedCeChunks : 4;
+  int wantChunks = c->fusedCeChunks > 0 ? c->fusedCeChunks : (c->cfg.fusedCeChunks > 0 ? c->cfg.fusedCeChunks : 2);
   if (const char* e = getenv("UCCL_FUSED_CE_CHUNKS")) {  // read per call so that a tuning run can vary it
     if (atoi(e) > 0) wantChunks = atoi(e);
   }

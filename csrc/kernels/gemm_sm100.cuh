@@ -633,7 +633,7 @@ __device__ void reduce_scatter_tail(const Args& a, uint8_t* smem, uint64_t* tbar
 
 // ------------------------------------------------------------------ epilogue of one tile, one warp
 // `taddr` addresses this warp's 32 TMEM lanes of the accumulator; `mb` is the 128-row block.
-template <int EPI, int COMM>
+template <int EPI, int COMM, int NBUF>
 __device__ __forceinline__ void epilogue_tile(const Args& a, const PeerMaps& pm, uint32_t taddr, int mb, int nb, int q,
                                               int lane, uint8_t* stage, uint32_t& stage_it) {
   const int row = mb * BM + q * 32 + lane;
@@ -649,9 +649,9 @@ __device__ __forceinline__ void epilogue_tile(const Args& a, const PeerMaps& pm,
       ptx::tmem_ld_32x32b_x32(taddr + g * 64, r0);
       ptx::tmem_ld_32x32b_x32(taddr + g * 64 + 32, r1);
       ptx::tmem_ld_wait();
-      uint8_t* buf = stage + (stage_it & 1) * EPI_BUF_BYTES;
+      uint8_t* buf = stage + (stage_it % NBUF) * EPI_BUF_BYTES;
       ++stage_it;
-      if (lane == 0) ptx::tma_store_wait_read<1>();  // the store that last used this buffer has read it
+      if (lane == 0) ptx::tma_store_wait_read<NBUF - 1>();  // the store that last used this buffer has read it
       __syncwarp();
       uint8_t* myrow = buf + lane * 128;
 #pragma unroll
@@ -891,7 +891,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (!ptx::mbar_wait_bounded(&tfull_bar[acc], acc_ph, bail)) break;
       ptx::tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
-      epilogue_tile<EPI, COMM>(a, pm, taddr, mb, nb, q, lane, stage, stage_it);
+      epilogue_tile<EPI, COMM, 2>(a, pm, taddr, mb, nb, q, lane, stage, stage_it);
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&tempty_bar[acc]);
@@ -929,6 +929,12 @@ template <int EPI, int COMM>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ PeerMaps pm, const Args a) {
+  // The reduce-scatter fusion trades one pipeline stage for a deeper epilogue staging area: a
+  // whole tile (4 x 4 KiB per warp) can be handed to the TMA without waiting for earlier stores,
+  // which decouples the accumulator hand-back from the pace of the links.
+  constexpr int ST = COMM == kCommReduceScatter ? pair::STAGES - 1 : pair::STAGES;
+  constexpr int NBUF = COMM == kCommReduceScatter ? 4 : 2;
+  constexpr int EPI_OFF = COMM == kCommReduceScatter ? ST * pair::STAGE_BYTES : PIPE_BYTES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PIPE_BYTES + EPI_STAGE_BYTES);
@@ -941,10 +947,10 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   }
   const int cta_id = static_cast<int>(blockIdx.x) - a.comm_ctas;
   uint64_t* full_bar = bars;                           // [STAGES]  used in the leader
-  uint64_t* empty_bar = bars + pair::STAGES;           // [STAGES]  one per CTA
-  uint64_t* tfull_bar = bars + 2 * pair::STAGES;       // [2]       one per CTA
-  uint64_t* tempty_bar = bars + 2 * pair::STAGES + 2;  // [2]       used in the leader
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * pair::STAGES + 4);
+  uint64_t* empty_bar = bars + ST;           // [STAGES]  one per CTA
+  uint64_t* tfull_bar = bars + 2 * ST;       // [2]       one per CTA
+  uint64_t* tempty_bar = bars + 2 * ST + 2;  // [2]       used in the leader
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * ST + 4);
   volatile uint32_t* bail = tmem_holder + 1;
   uint32_t* warps_done = tmem_holder + 2;
 
@@ -960,7 +966,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   const int num_kb = (a.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < pair::STAGES; ++s) {
+    for (int s = 0; s < ST; ++s) {
       ptx::mbar_init(&full_bar[s], 1);   // the leader's arrive.expect_tx; bytes come from both CTAs
       ptx::mbar_init(&empty_bar[s], 1);  // one tcgen05.commit from the leader
     }
@@ -1015,8 +1021,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         if (EPI == kEpiSwiGLU) brow = (leader ? 0 : a.b_half_rows) + nb * (BN / 2);  // gate | up
         else brow = nb * BN + static_cast<int>(crank) * (BN / 2);
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % pair::STAGES;
-          const uint32_t ph = (it / pair::STAGES) & 1;
+          const int s = it % ST;
+          const uint32_t ph = (it / ST) & 1;
           if (!ptx::mbar_wait_bounded(&empty_bar[s], ph ^ 1, bail)) break;
           uint8_t* sA = smem + s * pair::STAGE_BYTES;
           uint8_t* sB = sA + pair::A_BYTES;
@@ -1038,8 +1044,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % pair::STAGES;
-          const uint32_t ph = (it / pair::STAGES) & 1;
+          const int s = it % ST;
+          const uint32_t ph = (it / ST) & 1;
           if (!ptx::mbar_wait_bounded(&full_bar[s], ph, bail)) break;
           ptx::tc_fence_after();
           const uint32_t sA = ptx::smem_u32(smem + s * pair::STAGE_BYTES);
@@ -1061,7 +1067,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   } else {
     // ------------------------------------------------------------ epilogue warps (both CTAs)
     const int q = warp & 3;
-    uint8_t* stage = smem + PIPE_BYTES + q * 2 * EPI_BUF_BYTES;
+    uint8_t* stage = smem + EPI_OFF + q * NBUF * EPI_BUF_BYTES;
     uint32_t tcount = 0, stage_it = 0;
     int prev_mb = 0;
     for (int tile = pair_id; tile < num_tiles && !*bail; tile += pairs, ++tcount) {
@@ -1072,7 +1078,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       if (!ptx::mbar_wait_bounded(&tfull_bar[acc], acc_ph, bail)) break;
       ptx::tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
-      epilogue_tile<EPI, COMM>(a, pm, taddr, mb, nb, q, lane, stage, stage_it);
+      epilogue_tile<EPI, COMM, NBUF>(a, pm, taddr, mb, nb, q, lane, stage, stage_it);
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive_cluster(tempty0 + acc * 8);

@@ -37,13 +37,21 @@ __global__ void __launch_bounds__(kMoeThreads) moe_dispatch_kernel(const __grid_
     const char* row = static_cast<const char*>(a.x) + static_cast<size_t>(t) * H * 2;
     uint2 q[kMoeMaxIter];
     float scaleLo = 0.f, scaleHi = 0.f;  // lane l ends up with the scales of blocks l and 32 + l
+    // the row is read in batches of eight 16-byte loads per lane, all issued before the first use
+    constexpr int kBatch = 8;
+    uint4 vb[kBatch];
 #pragma unroll
     for (int i = 0; i < kMoeMaxIter; ++i) {
+      if ((i % kBatch) == 0) {
+#pragma unroll
+        for (int j = 0; j < kBatch; ++j) {
+          vb[j] = make_uint4(0, 0, 0, 0);
+          if (i + j < iters && 2 * (i + j) + half < nblk)
+            vb[j] = ptx::ld_global_v4(row + (static_cast<size_t>(i + j) * 256 + lane * 8) * 2);
+        }
+      }
       if (i < iters) {
-        const int blk = 2 * i + half;
-        const bool live = blk < nblk;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (live) v = ptx::ld_global_v4(row + (static_cast<size_t>(i) * 256 + lane * 8) * 2);
+        const uint4 v = vb[i % kBatch];
         float f[8];
         const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll

@@ -269,6 +269,11 @@ class Communicator:
         """Force the CTA count of collective kernels (0 = let the tuner decide)."""
         _C.set_blocks(self._comm, int(blocks))
 
+    def set_fused_options(self, ag_mode: str = "auto", comm_ctas: int = 0, ce_chunks: int = 0):
+        """How the all-gather -> GEMM fusion moves its rows: ``"ce"`` (copy engines, ``ce_chunks`` copies per
+        peer) or ``"kernel"`` (``comm_ctas`` communication CTAs inside the GEMM launch); 0 keeps a default."""
+        _C.set_fused_options(self._comm, {"auto": 0, "ce": 1, "kernel": 2}[ag_mode], int(comm_ctas), int(ce_chunks))
+
     def load_tuning(self, path: str):
         _C.load_tuning(self._comm, path)
 

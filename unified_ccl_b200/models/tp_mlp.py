@@ -47,6 +47,36 @@ class TensorParallelMLP:
 
     __call__ = forward
 
+    # candidates of autotune(): (all-gather mode, communication CTAs, copy-engine chunks per peer)
+    AG_CANDIDATES = (("ce", 0, 1), ("ce", 0, 2), ("ce", 0, 4), ("kernel", 8, 0), ("kernel", 16, 0), ("kernel", 24, 0))
+
+    def autotune(self, x_shard: torch.Tensor, iters: int = 3, candidates=None):
+        """Times the all-gather -> GEMM half of the block under each candidate setting (CUDA events,
+        summed over the ranks so that every rank takes the same decision) and keeps the fastest.
+        Returns ``{candidate: microseconds averaged over ranks}``; a no-op on one rank."""
+        if self.tp == 1:
+            return {}
+        cands = tuple(candidates or self.AG_CANDIDATES)
+        times = torch.zeros(len(cands), device=self.h.device, dtype=torch.float32)
+        stream = torch.cuda.current_stream(self.h.device)
+        for i, (mode, ctas, chunks) in enumerate(cands):
+            self.comm.set_fused_options(mode, ctas, chunks)
+            allgather_gemm(self.comm, x_shard, self.x_full, self.w_gate_up, out=self.h, swiglu=True)  # warm-up
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record(stream)
+            for _ in range(iters):
+                allgather_gemm(self.comm, x_shard, self.x_full, self.w_gate_up, out=self.h, swiglu=True)
+            e.record(stream)
+            e.synchronize()
+            times[i] = s.elapsed_time(e) * 1e3 / iters
+        self.comm.allreduce(times)
+        stream.synchronize()
+        avg = (times / self.tp).tolist()
+        best = min(range(len(cands)), key=lambda i: avg[i])
+        self.comm.set_fused_options(*cands[best])
+        self.ag_choice = cands[best]
+        return {cands[i]: round(avg[i], 1) for i in range(len(cands))}
+
     def reference(self, x_full: torch.Tensor) -> torch.Tensor:
         """fp32 PyTorch restatement of this rank's partial result (before the reduce-scatter)."""
         fs = self.ffn // self.tp
