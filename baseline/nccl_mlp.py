@@ -12,7 +12,8 @@ class NcclCublasMLP:
         self.x_full = torch.empty(tokens, hidden, device=dev, dtype=torch.bfloat16)
         self.y = torch.empty(tokens // tp, hidden, device=dev, dtype=torch.bfloat16)
 
-    def forward(self, x_shard: torch.Tensor) -> torch.Tensor:
+    def up(self, x_shard: torch.Tensor) -> torch.Tensor:
+        """all-gather, up/gate GEMM, SwiGLU"""
         if self.tp > 1:
             dist.all_gather_into_tensor(self.x_full, x_shard)
             x = self.x_full
@@ -20,11 +21,19 @@ class NcclCublasMLP:
             x = x_shard
         gu = torch.matmul(x, self.w_gate_up.t())
         f = gu.shape[1] // 2
-        h = torch.nn.functional.silu(gu[:, :f]) * gu[:, f:]
-        part = torch.matmul(h, self.w_down.t())
+        self.h = torch.nn.functional.silu(gu[:, :f]) * gu[:, f:]
+        return self.h
+
+    def down(self) -> torch.Tensor:
+        """down GEMM, reduce-scatter"""
+        part = torch.matmul(self.h, self.w_down.t())
         if self.tp > 1:
             dist.reduce_scatter_tensor(self.y, part)
             return self.y
         return part
+
+    def forward(self, x_shard: torch.Tensor) -> torch.Tensor:
+        self.up(x_shard)
+        return self.down()
 
     __call__ = forward

@@ -129,6 +129,15 @@ def main():
     torch.cuda.synchronize()
     rel = ((y - yb).abs().max() / yb.abs().max().clamp_min(1e-6)).item()
 
+    # ---- the two halves of the block on their own (untimed extra; explains the headline number)
+    halves = {}
+    if world > 1:
+        from unified_ccl_b200.parallel import allgather_gemm, gemm_reduce_scatter
+        halves["ag_gemm_us"] = round(1e3 * timed(lambda: allgather_gemm(comm, x_dev, mlp.x_full, mlp.w_gate_up, out=mlp.h, swiglu=True), 10, 3), 1)
+        halves["gemm_rs_us"] = round(1e3 * timed(lambda: gemm_reduce_scatter(comm, mlp.h, mlp.w_down, mlp.c_partial, out=mlp.y), 10, 3), 1)
+        halves["nccl_ag_cublas_us"] = round(1e3 * timed(lambda: base.up(x_dev), 10, 3), 1)
+        halves["cublas_nccl_rs_us"] = round(1e3 * timed(lambda: base.down(), 10, 3), 1)
+
     # ---- all-reduce sample against NCCL (bus bandwidth, bf16, symmetric buffers)
     sweep = []
     if world > 1 and not args.no_sweep:
@@ -189,6 +198,7 @@ def main():
             "allreduce_vs_nccl": sweep,
             "comm": {k: comm.info[k] for k in ("nvls", "p2p_mode", "net_active")},
             "ag_gemm_autotune_us": autotune,
+            "halves": halves,
         }
         print(json.dumps(out))
     barrier()

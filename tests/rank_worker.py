@@ -263,7 +263,10 @@ def case_fused_norm(comm, rank, n, args):
         gamma = (1 + 0.02 * torch.randn(hidden, generator=torch.Generator().manual_seed(8))).to(torch.bfloat16)
         h = (sum(x.float() for x in xs) + res.float()).to(torch.bfloat16).float()
         ref = h * torch.rsqrt((h * h).mean(-1, keepdim=True) + eps) * gamma.float()
-        for sym in (True, False):
+        # both data paths (multimem through the switch, plain peer loads / stores) at every size
+        algos = ("auto", "nvls", "two_shot") if (n > 1 and comm.info["nvls"]) else ("auto",)
+        for sym, algo in [(s_, a_) for s_ in (True, False) for a_ in algos]:
+            comm.set_algo(algo)
             x = comm.empty((tokens, hidden), torch.bfloat16) if sym else torch.empty(tokens, hidden, dtype=torch.bfloat16, device=dev)
             x.copy_(xs[rank])
             r_in = res.to(dev)
@@ -274,10 +277,11 @@ def case_fused_norm(comm, rank, n, args):
             e2 = (out.float().cpu() - ref).abs().max().item()
             # partial sums are rounded to bf16 once more when the switch reduces them
             if e1 > 0.13 * max(1.0, h.abs().max().item()) / 8 or e2 > 0.06:
-                fail.append((tokens, hidden, sym, e1, e2))
+                fail.append((tokens, hidden, sym, algo, e1, e2))
             if sym:
                 comm.free(x)
                 comm.free(r_out)
+        comm.set_algo("auto")
     return {"fail": fail}
 
 
@@ -287,7 +291,7 @@ def case_tp_mlp(comm, rank, n, args):
     dev = _dev(comm, rank)
     fail = []
     # both ways of moving the all-gather's rows: copy engines next to the GEMM, and CTAs inside it
-    for ag_mode in ("ce", "kernel"):
+    for ag_mode in (("ce", "kernel") if n > 1 else ("ce",)):
         os.environ["UCCL_FUSED_AG"] = ag_mode
         for hidden, ffn, tokens in ((512, 1024, 256 * n), (1024, 3584 * 2, 128 * n)):
             mlp = TensorParallelMLP(comm, hidden, ffn, tokens, seed=3)
@@ -297,7 +301,7 @@ def case_tp_mlp(comm, rank, n, args):
             for it in range(3):  # repeated calls reuse flags and scratch buffers
                 y = mlp(x_shard)
             _sync(comm)
-            gathered = mlp.x_full.clone()
+            gathered = mlp.x_full.clone() if n > 1 else x_full
             part = mlp.reference(x_full).contiguous()
             comm.allreduce(part)
             _sync(comm)
