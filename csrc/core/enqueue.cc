@@ -423,7 +423,9 @@ TuneChoice chooseFor(Comm* c, ucclCollKind_t kind, size_t bytes, bool symmetric,
   q.symmetric = symmetric;
   q.reducible = reducible(dt);
   q.netOnly = c->useNet || !c->p2pReady;
-  q.copyEngine = c->cfg.execMode == EXEC_COPY_ENGINE;
+  // copy_engine: copy engines move every byte (a small kernel reduces where the collective reduces);
+  // hybrid: the same from 1 MiB up, SM kernels below, where the engines' start-up cost dominates
+  q.copyEngine = c->cfg.execMode == EXEC_COPY_ENGINE || (c->cfg.execMode == EXEC_HYBRID && bytes >= (1u << 20));
   q.forcedAlgo = c->forcedAlgo;
   q.forcedProto = c->forcedProto;
   q.maxBlocks = c->cfg.maxCtas;

@@ -57,15 +57,22 @@ int fusedCommCtas(Comm* c) {
   return c->cfg.maxCtas > 0 ? std::min(c->cfg.maxCtas, 32) : 8;
 }
 
-// How the all-gather of the all-gather -> GEMM fusion moves its rows: copy engines next to the
-// GEMM (default: no SM is taken from the GEMM) or communication CTAs inside the launch
-// (UCCL_FUSED_AG=kernel, ucclCommSetFusedOptions, or an SM algorithm forced on the communicator).
-bool fusedAgByCopyEngine(Comm* c) {
+// How the all-gather of the all-gather -> GEMM fusion moves its rows:
+//   1 copy engines next to the GEMM (default: no SM work at all),
+//   2 dedicated communication CTAs inside the launch,
+//   3 "spread": a forwarder warp in every GEMM CTA.
+// UCCL_FUSED_AG=ce|kernel|spread wins over ucclCommSetFusedOptions; an SM algorithm forced on the
+// communicator selects 3.
+int fusedAgMode(Comm* c) {
   const char* s = getenv("UCCL_FUSED_AG");
-  if (s && *s) return !strcasecmp(s, "ce") || !strcasecmp(s, "copy_engine");
-  if (c->fusedAgMode != 0) return c->fusedAgMode == 1;
-  if (c->forcedAlgo == ucclAlgoOneShot || c->forcedAlgo == ucclAlgoTwoShot || c->forcedAlgo == ucclAlgoRing) return false;
-  return true;
+  if (s && *s) {
+    if (!strcasecmp(s, "ce") || !strcasecmp(s, "copy_engine")) return 1;
+    if (!strcasecmp(s, "kernel") || !strcasecmp(s, "ctas")) return 2;
+    if (!strcasecmp(s, "spread")) return 3;
+  }
+  if (c->fusedAgMode != 0) return c->fusedAgMode;
+  if (c->forcedAlgo == ucclAlgoOneShot || c->forcedAlgo == ucclAlgoTwoShot || c->forcedAlgo == ucclAlgoRing) return 3;
+  return 1;
 }
 
 // UCCL_FUSED_SELF=1 runs the fused kernels on a one-rank communicator too (every "peer" is this
@@ -232,7 +239,8 @@ extern "C" ucclResult_t ucclAllGatherGemm(const void* xShard, void* xFull, const
   }
   // Two ways to move the rows: communication CTAs inside the GEMM launch (default), or copy
   // engines on side streams next to it (UCCL_FUSED_AG=ce, or algorithm copy_engine forced).
-  if (fusedAgByCopyEngine(c)) {
+  const int agMode = fusedAgMode(c);
+  if (agMode == 1) {
     commCount(c, ucclCollAllGather, static_cast<size_t>(M) * K * 2, ucclAlgoCopyEngine);
     f.a_external = 1;
     char* fullPeer[UCCL_MAX_LOCAL_RANKS];
@@ -247,6 +255,7 @@ extern "C" ucclResult_t ucclAllGatherGemm(const void* xShard, void* xFull, const
     return allGatherPushEnd(c, !f.a_inplace, s);
   }
   commCount(c, ucclCollAllGather, static_cast<size_t>(M) * K * 2, ucclAlgoOneShot);
+  f.a_spread = agMode == 3 ? 1 : 0;
   // The kernel reads my rows from the shard; a copy engine puts them into xFull meanwhile.
   if (!f.a_inplace && (r = sideCopyBegin(c, const_cast<char*>(myRows), xShard, shardBytes, s)) != ucclSuccess) return r;
   if ((r = launchGemmBf16(g, &f, s)) != ucclSuccess) return r;

@@ -560,7 +560,7 @@ extern "C" ucclResult_t ucclCommSetAlgo(ucclComm_t comm, ucclAlgo_t algo, ucclPr
 extern "C" ucclResult_t ucclCommSetFusedOptions(ucclComm_t comm, int agMode, int commCtas, int ceChunks) {
   Comm* c = toComm(comm);
   if (!commValid(c)) return ucclInvalidArgument;
-  if (agMode < 0 || agMode > 2 || commCtas < 0 || commCtas > 64 || ceChunks < 0 || ceChunks > 64) return ucclInvalidArgument;
+  if (agMode < 0 || agMode > 3 || commCtas < 0 || commCtas > 64 || ceChunks < 0 || ceChunks > 64) return ucclInvalidArgument;
   c->fusedAgMode = agMode;
   c->fusedCommCtas = commCtas;
   c->fusedCeChunks = ceChunks;

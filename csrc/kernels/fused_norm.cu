@@ -141,7 +141,11 @@ __global__ void __launch_bounds__(kThreads, 1) ar_norm_kernel(const __grid_const
 
   size_t myOff, myLen;
   split(static_cast<size_t>(a.tokens), n, me, &myOff, &myLen);
-  // ---- phase A: my rows, R at a time (rows b, b+B, ... of my shard)
+  // ---- phase A: my rows (rows b, b+B, ... of my shard).  Through the switch one row per pass is
+  // enough to cover the latency (the links, not the loads in flight, are the limit) and lets the
+  // stores of one pass travel while the loads of the next are already out; the peer path takes R.
+  const NormPass npB = np;
+  if (a.inMc) np.R = 1;
   for (size_t r0 = b; r0 < ((a.debug & 4) ? 0 : myLen); r0 += static_cast<size_t>(B) * np.R) {
     size_t rowIdx[kNormMaxRows];
     int rowsHere = 0;
@@ -201,20 +205,20 @@ __global__ void __launch_bounds__(kThreads, 1) ar_norm_kernel(const __grid_const
     const int p = (me + q) % n;
     size_t ro, rl;
     split(static_cast<size_t>(a.tokens), n, p, &ro, &rl);
-    for (size_t r0 = b; r0 < rl; r0 += static_cast<size_t>(B) * np.R) {
+    for (size_t r0 = b; r0 < rl; r0 += static_cast<size_t>(B) * npB.R) {
       size_t rowIdx[kNormMaxRows];
       int rowsHere = 0;
 #pragma unroll
       for (int j = 0; j < kNormMaxRows; ++j) {
         const size_t r = r0 + static_cast<size_t>(j) * B;
         rowIdx[j] = ro + (r < rl ? r : r0);
-        if (j < np.R && r < rl) rowsHere = j + 1;
+        if (j < npB.R && r < rl) rowsHere = j + 1;
       }
       uint4 h[kNormSlots];
 #pragma unroll
       for (int s = 0; s < kNormSlots; ++s) {
         int j, v;
-        if (np.slot(s, rowsHere, &j, &v) && v < vecPerRow) {
+        if (npB.slot(s, rowsHere, &j, &v) && v < vecPerRow) {
           size_t row = rowIdx[0];
 #pragma unroll
           for (int jj = 1; jj < kNormMaxRows; ++jj)
@@ -224,7 +228,7 @@ __global__ void __launch_bounds__(kThreads, 1) ar_norm_kernel(const __grid_const
           h[s] = make_uint4(0, 0, 0, 0);
         }
       }
-      normalise_rows(np, h, rowsHere, rowIdx, a.gamma, a.outLocal, rowBytes, a.eps, a.hidden);
+      normalise_rows(npB, h, rowsHere, rowIdx, a.gamma, a.outLocal, rowBytes, a.eps, a.hidden);
     }
   }
   // staged residual: hand the rows back to the user's buffer

@@ -63,24 +63,26 @@ cudaError_t ensureSmem(Kern kern, int* last_dev, cudaError_t* err) {
 template <int EPI, int COMM>
 cudaError_t launchT(const CUtensorMap& tmA, const CUtensorMap& tmB, const gemm::PeerMaps& pm, const gemm::Args& args,
                     int grid, cudaStream_t stream) {
+  const int threads = (COMM == gemm::kCommAllGather && args.a_spread) ? gemm::NUM_THREADS_FWD : gemm::NUM_THREADS;
   auto kern = gemm::gemm_bf16_kernel<EPI, COMM>;
   static thread_local int last_dev = -1;
   static thread_local cudaError_t attr_err = cudaSuccess;
   cudaError_t e = ensureSmem(kern, &last_dev, &attr_err);
   if (e != cudaSuccess) return e;
-  kern<<<grid, gemm::NUM_THREADS, gemm::SMEM_BYTES, stream>>>(tmA, tmB, pm, args);
+  kern<<<grid, threads, gemm::SMEM_BYTES, stream>>>(tmA, tmB, pm, args);
   return cudaGetLastError();
 }
 
 template <int EPI, int COMM>
 cudaError_t launchPairT(const CUtensorMap& tmA, const CUtensorMap& tmB, const gemm::PeerMaps& pm,
                         const gemm::Args& args, int grid, cudaStream_t stream) {
+  const int threads = (COMM == gemm::kCommAllGather && args.a_spread) ? gemm::NUM_THREADS_FWD : gemm::NUM_THREADS;
   auto kern = gemm::gemm2_bf16_kernel<EPI, COMM>;
   static thread_local int last_dev = -1;
   static thread_local cudaError_t attr_err = cudaSuccess;
   cudaError_t e = ensureSmem(kern, &last_dev, &attr_err);
   if (e != cudaSuccess) return e;
-  kern<<<grid, gemm::NUM_THREADS, gemm::SMEM_BYTES, stream>>>(tmA, tmB, pm, args);
+  kern<<<grid, threads, gemm::SMEM_BYTES, stream>>>(tmA, tmB, pm, args);
   return cudaGetLastError();
 }
 
@@ -177,7 +179,7 @@ ucclResult_t launchGemmBf16(const GemmLaunch& g, const GemmFusion* f, cudaStream
     const int blk_per_rank = f->rows_per_rank / gemm::BM;
     a.m_bpr = blk_per_rank;
     if (role == gemm::kCommAllGather) {
-      comm_ctas = f->a_external ? 0 : std::max(1, std::min(f->comm_ctas > 0 ? f->comm_ctas : 8, sms / 4));
+      comm_ctas = (f->a_external || f->a_spread) ? 0 : std::max(1, std::min(f->comm_ctas > 0 ? f->comm_ctas : 8, sms / 4));
       for (int i = 0; i < f->nranks; ++i) {
         c.a_full_peer[i] = static_cast<char*>(f->a_full_peer[i]);
         c.ready_peer[i] = f->ready_peer[i];
@@ -187,16 +189,10 @@ ucclResult_t launchGemmBf16(const GemmLaunch& g, const GemmFusion* f, cudaStream
       a.a_ready = f->ready_peer[f->rank];
       // one count per copied piece of a row block (see comm_allgather_push / _push2d)
       const size_t blkBytes = static_cast<size_t>(gemm::BM) * g.K * 2;
-      a.a_push2d = (a.debug & 4096) ? 1 : 0;
-      if (f->a_external) {
-        a.a_ready_target = 1;
-      } else if (a.a_push2d) {
-        a.a_ready_target = static_cast<uint32_t>((g.K + gemm::BK - 1) / gemm::BK);
-        for (int i = 0; i < f->nranks; ++i)
-          if (!makeTensorMap(&pm.m[1 + i], f->a_full_peer[i], g.M, g.K, g.K, gemm::BK, gemm::BM)) return ucclSystemError;
-      } else {
-        a.a_ready_target = static_cast<uint32_t>((blkBytes + gemm::COPY_SLOT_BYTES - 1) / gemm::COPY_SLOT_BYTES);
-      }
+      a.a_spread = (!f->a_external && f->a_spread) ? 1 : 0;
+      if (f->a_external) a.a_ready_target = 1;
+      else if (a.a_spread) a.a_ready_target = static_cast<uint32_t>((blkBytes + gemm::FWD_SLOT_BYTES - 1) / gemm::FWD_SLOT_BYTES);
+      else a.a_ready_target = static_cast<uint32_t>((blkBytes + gemm::COPY_SLOT_BYTES - 1) / gemm::COPY_SLOT_BYTES);
       a.a_local_lo = f->rank * blk_per_rank;
       a.a_local_hi = a.a_local_lo + blk_per_rank;
       if (!f->a_inplace) {
@@ -208,11 +204,13 @@ ucclResult_t launchGemmBf16(const GemmLaunch& g, const GemmFusion* f, cudaStream
     } else {
       for (int i = 0; i < f->nranks; ++i) {
         c.done_peer[i] = f->done_peer[i];
+        c.stage_peer[i] = static_cast<char*>(f->stage_peer[i]);
         // every rank's staging buffer is [nranks * rows_per_rank, N]: slot-major rows
         if (!makeTensorMap(&pm.m[i], f->stage_peer[i], static_cast<uint64_t>(f->nranks) * f->rows_per_rank, g.N, g.N, 64, 32))
           return ucclSystemError;
       }
       c.stage_local = static_cast<const char*>(f->stage_peer[f->rank]);
+      c.rs_plain_stores = ((a.debug & 256) && g.N % 64 == 0) ? 1 : 0;
       c.done_target = static_cast<uint32_t>(f->nranks * a.tiles_n);
       c.rs_out = static_cast<char*>(f->rs_out);
       c.rs_ldo = f->rs_ldo;

@@ -44,6 +44,7 @@ constexpr int BN = 256;
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
 constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS_FWD = 224;  // all-gather fusion: one more warp, the forwarder of "spread" mode
 constexpr int TMEM_COLS = 512;
 
 // single-CTA kernel: 4 stages of (A 16 KiB + B 32 KiB)
@@ -95,6 +96,8 @@ struct CommArgs {
   // reduce-scatter: every rank owns a staging buffer [nranks][rows_per_rank][N]; slot s receives
   // rank s's partial result for the owner's rows (tensor maps in PeerMaps)
   const char* stage_local = nullptr;
+  char* stage_peer[kMaxPeers] = {};     // every rank's staging buffer (plain-store variant of the epilogue)
+  int rs_plain_stores = 0;              // 1: coalesced st.global from the staged tile instead of TMA stores
   uint32_t* done_peer[kMaxPeers] = {};  // every rank's per-row-block counters, zero at launch
   uint32_t done_target = 0;             // nranks * column tiles
   char* rs_out = nullptr;               // [rows_per_rank, N] bf16
@@ -121,7 +124,7 @@ struct Args {
   const uint32_t* a_ready;  // optional arrival flags per 128-row block (local memory)
   uint32_t a_ready_target;
   int a_local_lo, a_local_hi;  // row blocks in [lo, hi) need no wait (my own rows)
-  int a_push2d;             // all-gather: tensor-map copies (pm.m[1 + p] maps rank p's A buffer)
+  int a_spread;             // all-gather: warp 6 of every GEMM CTA forwards a share of the shard
   int a_own_shard;          // all-gather: read my own rows through pm.m[0] (the shard) instead of A
   uint32_t* err;            // error word (mapped or device memory); 0 = ok
   unsigned long long* times;  // optional: CTA 0 records globaltimer stamps here (profiling aid)
@@ -134,26 +137,17 @@ struct Args {
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
 
 // Bounded wait until *flag >= target. Returns false on timeout / abort.
-// mode (experiments): 1 polls with gpu-scope loads, 2 pauses 4 us between polls.
-__device__ __forceinline__ uint32_t poll_u32(const uint32_t* flag, int mode) {
-  if (mode & 1) {
-    uint32_t v;
-    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-    return v;
-  }
-  return ptx::ld_relaxed_sys_u32(flag);
-}
+// Relaxed polls with a growing pause, one system-scope fence on success.
 __device__ __forceinline__ bool wait_flag_geq(const uint32_t* flag, uint32_t target, uint64_t timeout_ns,
-                                              const uint32_t* abort_flag, int mode = 0) {
-  // relaxed polls with a growing pause, one system-scope fence on success
-  if (poll_u32(flag, mode) >= target) {
+                                              const uint32_t* abort_flag) {
+  if (ptx::ld_relaxed_sys_u32(flag) >= target) {
     ptx::fence_sys();
     return true;
   }
   const uint64_t t0 = ptx::globaltimer_ns();
   uint32_t spins = 0, pause = 32;
   while (true) {
-    if (poll_u32(flag, mode) >= target) {
+    if (ptx::ld_relaxed_sys_u32(flag) >= target) {
       ptx::fence_sys();
       return true;
     }
@@ -161,7 +155,7 @@ __device__ __forceinline__ bool wait_flag_geq(const uint32_t* flag, uint32_t tar
       if (abort_flag && ptx::ld_relaxed_sys_u32(abort_flag)) return false;
       if (timeout_ns && ptx::globaltimer_ns() - t0 > timeout_ns) return false;
     }
-    __nanosleep((mode & 2) ? 4000 : pause);
+    __nanosleep(pause);
     if (pause < 1024) pause <<= 1;
   }
 }
@@ -199,26 +193,30 @@ __device__ __forceinline__ void tile_coords(const Args& a, int tile, int tiles_r
   mrow = order_rows(a, first + (r % gsz), tiles_rows, unit);
 }
 
-// ------------------------------------------------------------------ all-gather push (comm CTAs)
-// The shard is cut into pieces of COPY_SLOT_BYTES, dealt round-robin to the communication CTAs.
-// One elected thread per CTA runs a ring of six shared-memory slots: local bulk load of piece k+4,
-// bulk stores of piece k to every rank, and - four pieces later, when those stores have completed -
+// ------------------------------------------------------------------ all-gather push
+// The shard is cut into pieces of SLOT_BYTES, dealt round-robin to the participating CTAs.  One
+// thread per CTA runs a ring of SLOTS shared-memory slots: local bulk load of piece k+AHEAD, bulk
+// stores of piece k to every other rank, and - LAG pieces later, when those stores have completed -
 // the arrival counters of the piece's row block on every rank.
-__device__ __forceinline__ int pieces_per_block(const Args& a) {
-  const size_t blkBytes = static_cast<size_t>(BM) * a.K * 2;
-  return static_cast<int>((blkBytes + COPY_SLOT_BYTES - 1) / COPY_SLOT_BYTES);
-}
+// Two users: dedicated communication CTAs (six 32 KiB slots in the pipeline's shared memory), and
+// the forwarder warp that every GEMM CTA has in "spread" mode (four 8 KiB slots in the epilogue
+// staging area, which the all-gather fusion does not use).  A single SM sustains only about
+// 20 GB/s of remote stores, so the second form, which spreads the shard over all SMs and takes
+// none of them away from the GEMM, is the one that can fill the links.
+constexpr int FWD_SLOT_BYTES = 8 << 10;
+constexpr int FWD_SLOTS = 4;
 
+template <int SLOT_BYTES, int SLOTS, int AHEAD, int LAG>
 __device__ void comm_allgather_push(const Args& a, uint8_t* smem, uint64_t* bars, int cta, int nctas) {
-  if (threadIdx.x != 0) return;
+  static_assert(AHEAD < SLOTS, "some slots must be left to the stores");
   const CommArgs& c = a.comm;
   const int n = c.nranks, r = c.rank, bpr = a.m_bpr;
   const size_t blkBytes = static_cast<size_t>(BM) * a.K * 2;
-  const int nsub = pieces_per_block(a);
+  const int nsub = static_cast<int>((blkBytes + SLOT_BYTES - 1) / SLOT_BYTES);
   const int allPieces = bpr * nsub;
   const size_t shardOff = static_cast<size_t>(r) * bpr * blkBytes;
-  uint64_t* full = bars;  // COPY_SLOTS barriers
-  for (int s = 0; s < COPY_SLOTS; ++s) ptx::mbar_init(&full[s], 1);
+  uint64_t* full = bars;  // SLOTS barriers
+  for (int s = 0; s < SLOTS; ++s) ptx::mbar_init(&full[s], 1);
   ptx::mbar_fence_init();
   volatile uint32_t bail = 0;
   const int mapMode = (a.debug >> 10) & 3;  // experiments: 1 whole blocks per CTA, 2 one contiguous range per CTA
@@ -240,9 +238,9 @@ __device__ void comm_allgather_push(const Args& a, uint8_t* smem, uint64_t* bars
     const int g = piece(i);
     blk = g / nsub;
     const int sub = g - blk * nsub;
-    off = static_cast<size_t>(blk) * blkBytes + static_cast<size_t>(sub) * COPY_SLOT_BYTES;
-    const size_t left = blkBytes - static_cast<size_t>(sub) * COPY_SLOT_BYTES;
-    bytes = static_cast<uint32_t>(left < COPY_SLOT_BYTES ? left : COPY_SLOT_BYTES);
+    off = static_cast<size_t>(blk) * blkBytes + static_cast<size_t>(sub) * SLOT_BYTES;
+    const size_t left = blkBytes - static_cast<size_t>(sub) * SLOT_BYTES;
+    bytes = static_cast<uint32_t>(left < SLOT_BYTES ? left : SLOT_BYTES);
   };
   // arrival counters: one add per (row block, rank) covering this CTA's pieces of the block
   int curBlk = -1;
@@ -269,109 +267,32 @@ __device__ void comm_allgather_push(const Args& a, uint8_t* smem, uint64_t* bars
     ++cnt;
     if (i + 1 >= total || piece(i + 1) / nsub != blk) flush();
   };
-  constexpr int AHEAD = 4;  // loads in flight; the two remaining slots are being read by stores
   auto load = [&](int i) {
     size_t off; uint32_t bytes; int blk;
     where(i, off, bytes, blk);
-    const int slot = i % COPY_SLOTS;
+    const int slot = i % SLOTS;
     ptx::mbar_expect_tx(&full[slot], bytes);
-    ptx::bulk_load(smem + slot * COPY_SLOT_BYTES, c.a_shard + off, bytes, &full[slot]);
+    ptx::bulk_load(smem + slot * SLOT_BYTES, c.a_shard + off, bytes, &full[slot]);
   };
   for (int i = 0; i < AHEAD && i < total; ++i) load(i);
   for (int k = 0; k < total; ++k) {
     size_t off; uint32_t bytes; int blk;
     where(k, off, bytes, blk);
-    const int slot = k % COPY_SLOTS;
-    if (!ptx::mbar_wait_bounded(&full[slot], (k / COPY_SLOTS) & 1, &bail)) {
+    const int slot = k % SLOTS;
+    if (!ptx::mbar_wait_bounded(&full[slot], (k / SLOTS) & 1, &bail)) {
       if (a.err) atomicCAS(a.err, 0u, 0x41475000u | static_cast<uint32_t>(blk & 0xfff));
       ptx::tma_store_wait<0>();
       return;
     }
     for (int q = 1; q < n; ++q) {
       const int p = (r + 1 + (q - 1 + k) % (n - 1)) % n;  // start at a different rank for every piece
-      ptx::bulk_store(c.a_full_peer[p] + shardOff + off, smem + slot * COPY_SLOT_BYTES, bytes);
+      ptx::bulk_store(c.a_full_peer[p] + shardOff + off, smem + slot * SLOT_BYTES, bytes);
     }
     ptx::tma_store_commit();
-    ptx::tma_store_wait_read<COPY_SLOTS - AHEAD>();  // pieces <= k-2 have left shared memory
-    if (k + AHEAD < total) load(k + AHEAD);
-    if (k >= 4) {
-      ptx::tma_store_wait<4>();  // the stores of pieces <= k-4 have completed on every rank
-      completed(k - 4);
-    }
-  }
-  ptx::tma_store_wait<0>();
-  for (int i = total > 4 ? total - 4 : 0; i < total; ++i) completed(i);
-  flush();
-}
-
-// Tensor-map variant of the push: pieces are 128-row x 64-column boxes (16 KiB) moved with tiled
-// TMA loads and stores, so that the copies in flight are spread over 128 rows of the destination
-// instead of one contiguous 32 KiB run.  pm.m[0] maps the shard, pm.m[1 + p] rank p's A buffer.
-constexpr int BOX_SLOT_BYTES = BM * BK * 2;  // 16 KiB
-constexpr int BOX_SLOTS = 12;
-__device__ void comm_allgather_push2d(const Args& a, const CUtensorMap* tmA, const PeerMaps& pm, uint8_t* smem,
-                                      uint64_t* bars, int cta, int nctas) {
-  if (threadIdx.x != 0) return;
-  const CommArgs& c = a.comm;
-  const int n = c.nranks, r = c.rank, bpr = a.m_bpr;
-  const int nsub = (a.K + BK - 1) / BK;  // boxes per row block
-  const int allPieces = bpr * nsub;
-  uint64_t* full = bars;  // BOX_SLOTS barriers
-  for (int s = 0; s < BOX_SLOTS; ++s) ptx::mbar_init(&full[s], 1);
-  ptx::mbar_fence_init();
-  volatile uint32_t bail = 0;
-  int total = 0;
-  for (int g = cta; g < allPieces; g += nctas) ++total;
-  const CUtensorMap* src = c.a_inplace ? tmA : &pm.m[0];
-  const int srcRow0 = c.a_inplace ? r * bpr * BM : 0;
-  int curBlk = -1;
-  uint32_t cnt = 0;
-  auto flush = [&]() {
-    if (curBlk < 0 || cnt == 0) return;
-    ptx::fence_sys();
-    for (int q = 1; q < n; ++q) {
-      const int p = (r + q) % n;
-      ptx::red_relaxed_sys_add_u32(c.ready_peer[p] + static_cast<size_t>(r * bpr + curBlk) * FLAG_STRIDE, cnt);
-    }
-    cnt = 0;
-  };
-  auto completed = [&](int i) {
-    const int blk = (cta + i * nctas) / nsub;
-    if (blk != curBlk) {
-      flush();
-      curBlk = blk;
-    }
-    ++cnt;
-    const int gn = cta + (i + 1) * nctas;
-    if (gn >= allPieces || gn / nsub != blk) flush();
-  };
-  constexpr int AHEAD = 8, LAG = 8;
-  auto load = [&](int i) {
-    const int g = cta + i * nctas;
-    const int blk = g / nsub, cb = g - blk * nsub;
-    const int slot = i % BOX_SLOTS;
-    ptx::mbar_expect_tx(&full[slot], BOX_SLOT_BYTES);
-    ptx::tma_load_2d(smem + slot * BOX_SLOT_BYTES, src, &full[slot], cb * BK, srcRow0 + blk * BM);
-  };
-  for (int i = 0; i < AHEAD && i < total; ++i) load(i);
-  for (int k = 0; k < total; ++k) {
-    const int g = cta + k * nctas;
-    const int blk = g / nsub, cb = g - blk * nsub;
-    const int slot = k % BOX_SLOTS;
-    if (!ptx::mbar_wait_bounded(&full[slot], (k / BOX_SLOTS) & 1, &bail)) {
-      if (a.err) atomicCAS(a.err, 0u, 0x41475000u | static_cast<uint32_t>(blk & 0xfff));
-      ptx::tma_store_wait<0>();
-      return;
-    }
-    for (int q = 1; q < n; ++q) {
-      const int p = (r + 1 + (q - 1 + k) % (n - 1)) % n;
-      ptx::tma_store_2d(&pm.m[1 + p], smem + slot * BOX_SLOT_BYTES, cb * BK, (r * bpr + blk) * BM);
-    }
-    ptx::tma_store_commit();
-    ptx::tma_store_wait_read<BOX_SLOTS - AHEAD>();
+    ptx::tma_store_wait_read<SLOTS - AHEAD>();  // pieces <= k-2 have left shared memory
     if (k + AHEAD < total) load(k + AHEAD);
     if (k >= LAG) {
-      ptx::tma_store_wait<LAG>();
+      ptx::tma_store_wait<LAG>();  // the stores of pieces <= k-LAG have completed on every rank
       completed(k - LAG);
     }
   }
@@ -651,7 +572,7 @@ __device__ __forceinline__ void epilogue_tile(const Args& a, const PeerMaps& pm,
       ptx::tmem_ld_wait();
       uint8_t* buf = stage + (stage_it % NBUF) * EPI_BUF_BYTES;
       ++stage_it;
-      if (lane == 0) ptx::tma_store_wait_read<NBUF - 1>();  // the store that last used this buffer has read it
+      if (lane == 0 && !a.comm.rs_plain_stores) ptx::tma_store_wait_read<NBUF - 1>();  // the store that last used this buffer has read it
       __syncwarp();
       uint8_t* myrow = buf + lane * 128;
 #pragma unroll
@@ -664,9 +585,27 @@ __device__ __forceinline__ void epilogue_tile(const Args& a, const PeerMaps& pm,
         v.w = ptx::pack_bf16x2(__uint_as_float(s[6]), __uint_as_float(s[7]));
         *reinterpret_cast<uint4*>(myrow + ((k ^ (lane & 7)) << 4)) = v;  // 128-byte swizzle
       }
+      const int col0 = nb * BN + g * 64;
+      if (a.comm.rs_plain_stores) {
+        // plain stores: four rows x 128 contiguous bytes per warp instruction, posted writes that
+        // do not occupy the TMA unit
+        __syncwarp();
+        if (col0 + 64 <= a.N && !(a.debug & 2)) {
+          char* dbase = a.comm.stage_peer[(a.debug & 16) ? a.comm.rank : owner] +
+                        (static_cast<size_t>(drow) * a.N + col0) * 2;
+          const int cch = lane & 7;
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int rr = (lane >> 3) + 4 * it;
+            const uint4 v = *reinterpret_cast<const uint4*>(buf + rr * 128 + ((cch ^ (rr & 7)) << 4));
+            ptx::st_global_v4(dbase + static_cast<size_t>(rr) * a.N * 2 + (cch << 4), v);
+          }
+        }
+        __syncwarp();  // the buffer may be rewritten
+        continue;
+      }
       ptx::fence_proxy_async_smem();
       __syncwarp();
-      const int col0 = nb * BN + g * 64;
       if (lane == 0 && col0 < a.N && !(a.debug & 2)) {
         ptx::tma_store_2d(dmap, buf, col0, drow);
       }
@@ -741,8 +680,12 @@ __device__ __forceinline__ void epilogue_tile(const Args& a, const PeerMaps& pm,
 // the MMA warp needs all four to have drained accumulator t-2 before it can produce tile t.
 template <int PENDING>
 __device__ __forceinline__ void publish_tile(const Args& a, int mb, int lane, uint32_t* counter) {
+  if (a.comm.rs_plain_stores) {
+    ptx::fence_sys();  // every lane's own stores have been performed
+    __syncwarp();
+  }
   if (lane != 0) return;
-  ptx::tma_store_wait<PENDING>();
+  if (!a.comm.rs_plain_stores) ptx::tma_store_wait<PENDING>();
   __threadfence_block();
   const uint32_t old = atomicAdd(counter, 1u);
   if ((old & 3u) == 3u) {
@@ -754,17 +697,15 @@ __device__ __forceinline__ void publish_tile(const Args& a, int mb, int lane, ui
 
 // ------------------------------------------------------------------ single-CTA kernel
 template <int EPI, int COMM>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(COMM == kCommAllGather ? NUM_THREADS_FWD : NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ PeerMaps pm, const Args a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PIPE_BYTES + EPI_STAGE_BYTES);
   if (COMM == kCommAllGather && static_cast<int>(blockIdx.x) < a.comm_ctas) {
-    if (!(a.debug & 1)) {
-      if (a.a_push2d) comm_allgather_push2d(a, &tmA, pm, smem, bars, blockIdx.x, a.comm_ctas);
-      else comm_allgather_push(a, smem, bars, blockIdx.x, a.comm_ctas);
-    }
+    if (!(a.debug & 1) && threadIdx.x == 0)
+      comm_allgather_push<COPY_SLOT_BYTES, COPY_SLOTS, 4, 4>(a, smem, bars, blockIdx.x, a.comm_ctas);
     return;
   }
   const int cta_id = static_cast<int>(blockIdx.x) - a.comm_ctas;
@@ -818,7 +759,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const bool own = mb >= a.a_local_lo && mb < a.a_local_hi;
         if (a.a_ready && !(a.debug & 8) && !own) {
           if (!wait_flag_geq(a.a_ready + static_cast<size_t>(mb) * FLAG_STRIDE, a.a_ready_target, a.comm.timeout_ns,
-                             a.comm.abort_flag, (a.debug >> 8) & 3)) {
+                             a.comm.abort_flag)) {
             if (a.err) atomicCAS(a.err, 0u, 0x41470000u | static_cast<uint32_t>(mb));
             *bail = 1;
             break;
@@ -878,6 +819,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         ptx::umma_commit(&tfull_bar[acc]);
       }
     }
+  } else if (warp == 6) {
+    // ------------------------------------------------------------ forwarder (all-gather, spread mode)
+    if (COMM == kCommAllGather && a.a_spread && lane == 0 && !(a.debug & 1))
+      comm_allgather_push<FWD_SLOT_BYTES, FWD_SLOTS, 2, 2>(a, smem + PIPE_BYTES, bars + 24, blockIdx.x, gridDim.x);
   } else {
     // ------------------------------------------------------------ epilogue warps
     const int q = warp & 3;  // TMEM lane quarter this warp may access
@@ -926,7 +871,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 // instead of once per 128, which cuts shared-memory fill traffic by a third and leaves room for
 // six pipeline stages.
 template <int EPI, int COMM>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(COMM == kCommAllGather ? NUM_THREADS_FWD : NUM_THREADS, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ PeerMaps pm, const Args a) {
   // The reduce-scatter fusion trades one pipeline stage for a deeper epilogue staging area: a
@@ -939,10 +884,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PIPE_BYTES + EPI_STAGE_BYTES);
   if (COMM == kCommAllGather && static_cast<int>(blockIdx.x) < a.comm_ctas) {
-    if (!(a.debug & 1)) {
-      if (a.a_push2d) comm_allgather_push2d(a, &tmA, pm, smem, bars, blockIdx.x, a.comm_ctas);
-      else comm_allgather_push(a, smem, bars, blockIdx.x, a.comm_ctas);
-    }
+    if (!(a.debug & 1) && threadIdx.x == 0)
+      comm_allgather_push<COPY_SLOT_BYTES, COPY_SLOTS, 4, 4>(a, smem, bars, blockIdx.x, a.comm_ctas);
     return;
   }
   const int cta_id = static_cast<int>(blockIdx.x) - a.comm_ctas;
@@ -1006,7 +949,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         const bool own = mb >= a.a_local_lo && mb < a.a_local_hi;
         if (a.a_ready && !(a.debug & 8) && !own) {
           if (!wait_flag_geq(a.a_ready + static_cast<size_t>(mb) * FLAG_STRIDE, a.a_ready_target, a.comm.timeout_ns,
-                             a.comm.abort_flag, (a.debug >> 8) & 3)) {
+                             a.comm.abort_flag)) {
             if (a.err) atomicCAS(a.err, 0u, 0x41470000u | static_cast<uint32_t>(mb));
             *bail = 1;
             break;
@@ -1064,6 +1007,10 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         ptx::umma_commit_pair(tfull_peer + acc * 8);
       }
     }
+  } else if (warp == 6) {
+    // ------------------------------------------------------------ forwarder (all-gather, spread mode)
+    if (COMM == kCommAllGather && a.a_spread && lane == 0 && !(a.debug & 1))
+      comm_allgather_push<FWD_SLOT_BYTES, FWD_SLOTS, 2, 2>(a, smem + PIPE_BYTES, bars + 24, blockIdx.x, gridDim.x);
   } else {
     // ------------------------------------------------------------ epilogue warps (both CTAs)
     const int q = warp & 3;

@@ -245,6 +245,16 @@ def case_api_contract(comm, rank, n, args):
         pass
     if comm.rank != rank or comm.world_size != n:
         fail.append(("rank/world_size",))
+    # tuning knobs: accepted values stick, out-of-range values are refused
+    comm.set_fused_options("kernel", 12, 0)
+    comm.set_fused_options("ce", 0, 2)
+    comm.set_fused_options()
+    for bad in (("ce", 65, 0), ("ce", 0, 65), ("kernel", -1, 0)):
+        try:
+            comm.set_fused_options(*bad)
+            fail.append(("bad fused option accepted", bad))
+        except Exception:
+            pass
     comm.destroy()
     comm.destroy()  # idempotent
     return {"fail": fail}
@@ -290,8 +300,8 @@ def case_tp_mlp(comm, rank, n, args):
 
     dev = _dev(comm, rank)
     fail = []
-    # both ways of moving the all-gather's rows: copy engines next to the GEMM, and CTAs inside it
-    for ag_mode in (("ce", "kernel") if n > 1 else ("ce",)):
+    # every way of moving the all-gather's rows: copy engines, dedicated CTAs, a forwarder warp per CTA
+    for ag_mode in (("ce", "kernel", "spread") if n > 1 else ("ce",)):
         os.environ["UCCL_FUSED_AG"] = ag_mode
         for hidden, ffn, tokens in ((512, 1024, 256 * n), (1024, 3584 * 2, 128 * n)):
             mlp = TensorParallelMLP(comm, hidden, ffn, tokens, seed=3)

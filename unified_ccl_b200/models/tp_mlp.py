@@ -48,7 +48,7 @@ class TensorParallelMLP:
     __call__ = forward
 
     # candidates of autotune(): (all-gather mode, communication CTAs, copy-engine chunks per peer)
-    AG_CANDIDATES = (("ce", 0, 1), ("ce", 0, 2), ("ce", 0, 4), ("kernel", 8, 0), ("kernel", 16, 0), ("kernel", 24, 0))
+    AG_CANDIDATES = (("spread", 0, 0), ("ce", 0, 1), ("ce", 0, 2), ("ce", 0, 4), ("kernel", 8, 0), ("kernel", 16, 0), ("kernel", 24, 0))
 
     def autotune(self, x_shard: torch.Tensor, iters: int = 3, candidates=None):
         """Times the all-gather -> GEMM half of the block under each candidate setting (CUDA events,
