@@ -165,7 +165,7 @@ def main():
     link_gbs = 770.0
     ag_bytes = (world - 1) / world * tokens * HIDDEN * 2
     roof_us = max(flops / (peak_tflops * 1e12), 2 * ag_bytes / (link_gbs * 1e9) if world > 1 else 0.0) * 1e6
-    launches_per_step = 2 if world == 1 else 5  # gemm x2 (+ 3 rank-barrier kernels)
+    launches_per_step = 2 if world == 1 else 4  # two fused GEMM kernels (+ one rank-barrier kernel in front of each)
 
     if rank == 0:
         out = {

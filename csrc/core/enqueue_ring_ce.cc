@@ -79,8 +79,8 @@ ucclResult_t sideCopyBegin(Comm* c, void* dst, const void* src, size_t bytes, cu
 }
 // All-gather by copy engines for the all-gather -> GEMM fusion: this rank's shard goes to rows
 // [rank * rows, ...) of every rank's A buffer in `chunks` pieces per peer, each followed (in stream
-// order, on the same side stream) by a strided copy of ones onto the peer's arrival flags of the
-// row blocks it covers.  The GEMM kernel launched on `s` meanwhile polls those flags.  Call
+// order, on the same side stream) by a copy of ones onto the peer's arrival flags of the
+// row blocks it covers (one contiguous copy: flags are 128 bytes apart and the source has zeros in between).  The GEMM kernel launched on `s` meanwhile polls those flags.  Call
 // allGatherPushEnd after the kernel launch.
 ucclResult_t allGatherPushBegin(Comm* c, const void* shard, char* const* fullPeer, char* const* readyPeer,
                                 size_t shardBytes, int blocksPerRank, bool copyOwn, cudaStream_t s) {
@@ -116,10 +116,12 @@ ucclResult_t allGatherPushBegin(Comm* c, const void* shard, char* const* fullPee
       const int p = (me + q) % n;
       if (cudaMemcpyAsync(fullPeer[p] + rowOff + off, src + off, len, cudaMemcpyDeviceToDevice, c->ceStream[p]) != cudaSuccess)
         return cudaFail(c, "cudaMemcpyAsync");
-      if (cudaMemcpy2DAsync(readyPeer[p] + (static_cast<size_t>(me) * blocksPerRank + b0) * kGemmFlagStrideBytes,
-                            kGemmFlagStrideBytes, c->onesDev, kGemmFlagStrideBytes, sizeof(uint32_t), b1 - b0,
-                            cudaMemcpyDeviceToDevice, c->ceStream[p]) != cudaSuccess)
-        return cudaFail(c, "cudaMemcpy2DAsync");
+      // the flags of blocks b0..b1 in one contiguous copy: the source holds a one at every flag
+      // position and zeros in the padding between flags
+      if (cudaMemcpyAsync(readyPeer[p] + (static_cast<size_t>(me) * blocksPerRank + b0) * kGemmFlagStrideBytes, c->onesDev,
+                          static_cast<size_t>(b1 - b0) * kGemmFlagStrideBytes, cudaMemcpyDeviceToDevice,
+                          c->ceStream[p]) != cudaSuccess)
+        return cudaFail(c, "cudaMemcpyAsync");
     }
   }
   if (copyOwn &&

@@ -5,7 +5,7 @@
     y_shard = reduce_scatter(h @ Wd_r.T)           row-parallel,    Wd_r [H, F / tp]
 
 Both collectives run inside the GEMM kernels (all-gather -> GEMM with the SwiGLU epilogue, and
-GEMM -> reduce-scatter), so one forward pass is two kernel launches plus three tiny barriers.
+GEMM -> reduce-scatter), so one forward pass is two GEMM launches, each behind one small rank-barrier kernel.
 """
 import torch
 
