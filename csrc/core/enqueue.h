@@ -46,8 +46,8 @@ ucclResult_t sideCopyBegin(Comm* c, void* dst, const void* src, size_t bytes, cu
 ucclResult_t sideCopyEnd(Comm* c, cudaStream_t s);
 // copy-engine all-gather with per-row-block arrival flags (all-gather -> GEMM fusion)
 ucclResult_t allGatherPushBegin(Comm* c, const void* shard, char* const* fullPeer, char* const* readyPeer,
-                                size_t shardBytes, int blocksPerRank, bool copyOwn, cudaStream_t s);
-ucclResult_t allGatherPushEnd(Comm* c, bool copyOwn, cudaStream_t s);
+                                size_t shardBytes, int blocksPerRank, bool copyOwn, int lanes, cudaStream_t s);
+ucclResult_t allGatherPushEnd(Comm* c, bool copyOwn, int lanes, cudaStream_t s);
 ucclResult_t enqueueNetGpu(Comm* c, const CollOp& op);
 ucclResult_t enqueueNetGpuP2p(Comm* c, const std::vector<CollOp>& ops);
 

@@ -79,11 +79,33 @@ ucclResult_t sideCopyBegin(Comm* c, void* dst, const void* src, size_t bytes, cu
 }
 // All-gather by copy engines for the all-gather -> GEMM fusion: this rank's shard goes to rows
 // [rank * rows, ...) of every rank's A buffer in `chunks` pieces per peer, each followed (in stream
-// order, on the same side stream) by a copy of ones onto the peer's arrival flags of the
-// row blocks it covers (one contiguous copy: flags are 128 bytes apart and the source has zeros in between).  The GEMM kernel launched on `s` meanwhile polls those flags.  Call
-// allGatherPushEnd after the kernel launch.
+// order, on the same side stream) by a copy of ones onto the peer's arrival flags of the row
+// blocks it covers (one contiguous copy: flags are 128 bytes apart and the source has zeros in
+// between).  The GEMM kernel launched on `s` meanwhile polls those flags.
+// lanes == 0: one side stream per peer, all peers at once.  lanes > 0: that many streams, and the
+// peers are served in the order me-1, me-2, ... round-robin over the lanes, so that every rank
+// receives its shards one after the other, nearest first (from me+1, me+2, ...) - the order in
+// which the GEMM then visits them - instead of all of them at the very end.
+// Call allGatherPushEnd after the kernel launch.
+namespace {
+int cePushStreams(Comm* c, int lanes, bool copyOwn, cudaStream_t* out) {
+  const int n = c->localRanks, me = c->localRank;
+  int k = 0;
+  if (lanes <= 0) {
+    for (int p = 0; p < n; ++p)
+      if (p != me) out[k++] = c->ceStream[p];
+    if (copyOwn) out[k++] = c->ceStream[me];
+    return k;
+  }
+  const int used = std::min(lanes, n - 1);
+  for (int i = 0; i < used; ++i) out[k++] = c->ceStream[i];
+  if (copyOwn) out[k++] = c->ceStream[used];  // n streams exist and used <= n - 1
+  return k;
+}
+}  // namespace
+
 ucclResult_t allGatherPushBegin(Comm* c, const void* shard, char* const* fullPeer, char* const* readyPeer,
-                                size_t shardBytes, int blocksPerRank, bool copyOwn, cudaStream_t s) {
+                                size_t shardBytes, int blocksPerRank, bool copyOwn, int lanes, cudaStream_t s) {
   const ucclResult_t r = ensureCeStreams(c);
   if (r != ucclSuccess) return r;
   const int n = c->localRanks, me = c->localRank;
@@ -94,11 +116,11 @@ ucclResult_t allGatherPushBegin(Comm* c, const void* shard, char* const* fullPee
         cudaMemset2D(c->onesDev, kGemmFlagStrideBytes, 1, 1, kGemmMaxRowBlocks) != cudaSuccess)
       return cudaFail(c, "cudaMemset2D");
   }
+  cudaStream_t streams[UCCL_MAX_LOCAL_RANKS + 1];
+  const int nstreams = cePushStreams(c, lanes, copyOwn, streams);
   if (cudaEventRecord(c->ceStart, s) != cudaSuccess) return cudaFail(c, "cudaEventRecord");
-  for (int p = 0; p < n; ++p) {
-    if (p == me && !copyOwn) continue;
-    if (cudaStreamWaitEvent(c->ceStream[p], c->ceStart, 0) != cudaSuccess) return cudaFail(c, "cudaStreamWaitEvent");
-  }
+  for (int i = 0; i < nstreams; ++i)
+    if (cudaStreamWaitEvent(streams[i], c->ceStart, 0) != cudaSuccess) return cudaFail(c, "cudaStreamWaitEvent");
   const size_t blkBytes = shardBytes / blocksPerRank;
   int wantChunks = c->fusedCeChunks > 0 ? c->fusedCeChunks : (c->cfg.fusedCeChunks > 0 ? c->cfg.fusedCeChunks : 2);
   if (const char* e = getenv("UCCL_FUSED_CE_CHUNKS")) {  // read per call so that a tuning run can vary it
@@ -107,33 +129,47 @@ ucclResult_t allGatherPushBegin(Comm* c, const void* shard, char* const* fullPee
   const int chunks = std::min(wantChunks, blocksPerRank);
   const char* src = static_cast<const char*>(shard);
   const size_t rowOff = static_cast<size_t>(me) * shardBytes;
-  for (int j = 0; j < chunks; ++j) {
+  const int usedLanes = lanes > 0 ? std::min(lanes, n - 1) : 0;
+  auto pushChunk = [&](int p, int j, cudaStream_t st) -> ucclResult_t {
     const int b0 = static_cast<int>(static_cast<long long>(blocksPerRank) * j / chunks);
     const int b1 = static_cast<int>(static_cast<long long>(blocksPerRank) * (j + 1) / chunks);
-    if (b1 == b0) continue;
+    if (b1 == b0) return ucclSuccess;
     const size_t off = b0 * blkBytes, len = (b1 - b0) * blkBytes;
+    if (cudaMemcpyAsync(fullPeer[p] + rowOff + off, src + off, len, cudaMemcpyDeviceToDevice, st) != cudaSuccess)
+      return cudaFail(c, "cudaMemcpyAsync");
+    if (cudaMemcpyAsync(readyPeer[p] + (static_cast<size_t>(me) * blocksPerRank + b0) * kGemmFlagStrideBytes, c->onesDev,
+                        static_cast<size_t>(b1 - b0) * kGemmFlagStrideBytes, cudaMemcpyDeviceToDevice, st) != cudaSuccess)
+      return cudaFail(c, "cudaMemcpyAsync");
+    return ucclSuccess;
+  };
+  if (usedLanes == 0) {
+    for (int j = 0; j < chunks; ++j)
+      for (int q = 1; q < n; ++q) {
+        const int p = (me + q) % n;
+        const ucclResult_t rr = pushChunk(p, j, c->ceStream[p]);
+        if (rr != ucclSuccess) return rr;
+      }
+  } else {
     for (int q = 1; q < n; ++q) {
-      const int p = (me + q) % n;
-      if (cudaMemcpyAsync(fullPeer[p] + rowOff + off, src + off, len, cudaMemcpyDeviceToDevice, c->ceStream[p]) != cudaSuccess)
-        return cudaFail(c, "cudaMemcpyAsync");
-      // the flags of blocks b0..b1 in one contiguous copy: the source holds a one at every flag
-      // position and zeros in the padding between flags
-      if (cudaMemcpyAsync(readyPeer[p] + (static_cast<size_t>(me) * blocksPerRank + b0) * kGemmFlagStrideBytes, c->onesDev,
-                          static_cast<size_t>(b1 - b0) * kGemmFlagStrideBytes, cudaMemcpyDeviceToDevice,
-                          c->ceStream[p]) != cudaSuccess)
-        return cudaFail(c, "cudaMemcpyAsync");
+      const int p = (me - q + n) % n;  // rank p sees me at distance q
+      for (int j = 0; j < chunks; ++j) {
+        const ucclResult_t rr = pushChunk(p, j, c->ceStream[(q - 1) % usedLanes]);
+        if (rr != ucclSuccess) return rr;
+      }
     }
   }
-  if (copyOwn &&
-      cudaMemcpyAsync(fullPeer[me] + rowOff, src, shardBytes, cudaMemcpyDeviceToDevice, c->ceStream[me]) != cudaSuccess)
+  if (copyOwn && cudaMemcpyAsync(fullPeer[me] + rowOff, src, shardBytes, cudaMemcpyDeviceToDevice,
+                                 streams[nstreams - 1]) != cudaSuccess)
     return cudaFail(c, "cudaMemcpyAsync");
   return ucclSuccess;
 }
-ucclResult_t allGatherPushEnd(Comm* c, bool copyOwn, cudaStream_t s) {
-  for (int p = 0; p < c->localRanks; ++p) {
-    if (p == c->localRank && !copyOwn) continue;
-    if (cudaEventRecord(c->ceEvent[p], c->ceStream[p]) != cudaSuccess) return cudaFail(c, "cudaEventRecord");
-    if (cudaStreamWaitEvent(s, c->ceEvent[p], 0) != cudaSuccess) return cudaFail(c, "cudaStreamWaitEvent");
+ucclResult_t allGatherPushEnd(Comm* c, bool copyOwn, int lanes, cudaStream_t s) {
+  cudaStream_t streams[UCCL_MAX_LOCAL_RANKS + 1];
+  const int nstreams = cePushStreams(c, lanes, copyOwn, streams);
+  for (int i = 0; i < nstreams; ++i) {
+    // one event per stream: the events array has an entry for every local rank
+    if (cudaEventRecord(c->ceEvent[i], streams[i]) != cudaSuccess) return cudaFail(c, "cudaEventRecord");
+    if (cudaStreamWaitEvent(s, c->ceEvent[i], 0) != cudaSuccess) return cudaFail(c, "cudaStreamWaitEvent");
   }
   return ucclSuccess;
 }

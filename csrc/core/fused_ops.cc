@@ -249,10 +249,15 @@ extern "C" ucclResult_t ucclAllGatherGemm(const void* xShard, void* xFull, const
       fullPeer[p] = static_cast<char*>(f.a_full_peer[p]);
       readyPeer[p] = reinterpret_cast<char*>(f.ready_peer[p]);
     }
-    if ((r = allGatherPushBegin(c, xShard, fullPeer, readyPeer, shardBytes, rows / 128, !f.a_inplace, s)) != ucclSuccess)
+    // copy-engine lanes: UCCL_FUSED_CE_LANES, else the communicator's option (its commCtas field), else 0
+    int lanes = c->fusedCommCtas;
+    if (const char* e = getenv("UCCL_FUSED_CE_LANES")) lanes = atoi(e);
+    if (lanes < 0 || n <= 2) lanes = 0;
+    f.a_peer_major = lanes > 0 ? 1 : 0;
+    if ((r = allGatherPushBegin(c, xShard, fullPeer, readyPeer, shardBytes, rows / 128, !f.a_inplace, lanes, s)) != ucclSuccess)
       return r;
     if ((r = launchGemmBf16(g, &f, s)) != ucclSuccess) return r;
-    return allGatherPushEnd(c, !f.a_inplace, s);
+    return allGatherPushEnd(c, !f.a_inplace, lanes, s);
   }
   commCount(c, ucclCollAllGather, static_cast<size_t>(M) * K * 2, ucclAlgoOneShot);
   f.a_spread = agMode == 3 ? 1 : 0;

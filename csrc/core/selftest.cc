@@ -316,6 +316,10 @@ std::string testTuner() {
   q.bytes = 64u << 20;
   c = t.choose(q);
   EXPECT(c.algo == ucclAlgoNvls);
+  q.nranks = 2;  // the switch brings nothing between two GPUs
+  c = t.choose(q);
+  EXPECT(c.algo == ucclAlgoTwoShot);
+  q.nranks = 8;
   q.nvls = false;
   c = t.choose(q);
   EXPECT(c.algo == ucclAlgoTwoShot);

@@ -200,17 +200,15 @@ ucclResult_t launchGemmBf16(const GemmLaunch& g, const GemmFusion* f, cudaStream
         a.a_own_shard = 1;
         if (!makeTensorMap(&pm.m[0], f->a_shard, f->rows_per_rank, g.K, g.K, gemm::BK, gemm::BM)) return ucclSystemError;
       }
-      a.m_order = (a.debug & 4) ? 0 : 1;
+      a.m_order = (a.debug & 4) ? 0 : (f->a_peer_major ? 3 : 1);
     } else {
       for (int i = 0; i < f->nranks; ++i) {
         c.done_peer[i] = f->done_peer[i];
-        c.stage_peer[i] = static_cast<char*>(f->stage_peer[i]);
         // every rank's staging buffer is [nranks * rows_per_rank, N]: slot-major rows
         if (!makeTensorMap(&pm.m[i], f->stage_peer[i], static_cast<uint64_t>(f->nranks) * f->rows_per_rank, g.N, g.N, 64, 32))
           return ucclSystemError;
       }
       c.stage_local = static_cast<const char*>(f->stage_peer[f->rank]);
-      c.rs_plain_stores = ((a.debug & 256) && g.N % 64 == 0) ? 1 : 0;
       c.done_target = static_cast<uint32_t>(f->nranks * a.tiles_n);
       c.rs_out = static_cast<char*>(f->rs_out);
       c.rs_ldo = f->rs_ldo;

@@ -96,8 +96,6 @@ struct CommArgs {
   // reduce-scatter: every rank owns a staging buffer [nranks][rows_per_rank][N]; slot s receives
   // rank s's partial result for the owner's rows (tensor maps in PeerMaps)
   const char* stage_local = nullptr;
-  char* stage_peer[kMaxPeers] = {};     // every rank's staging buffer (plain-store variant of the epilogue)
-  int rs_plain_stores = 0;              // 1: coalesced st.global from the staged tile instead of TMA stores
   uint32_t* done_peer[kMaxPeers] = {};  // every rank's per-row-block counters, zero at launch
   uint32_t done_target = 0;             // nranks * column tiles
   char* rs_out = nullptr;               // [rows_per_rank, N] bf16
@@ -118,7 +116,8 @@ struct Args {
   int gemm_ctas;            // number of CTAs that run the GEMM roles
   int comm_ctas;            // CTAs [0, comm_ctas) run the communication role (scheduled first)
   int m_rot;                // row-block rotation: logical block i maps to (i + m_rot) % tiles_m
-  int m_order;              // 0: rotation only; 1: all-gather order; 2: reduce-scatter order
+  int m_order;              // 0: rotation only; 1: all-gather order; 2: reduce-scatter order;
+                            // 3: all-gather, one peer after the other
   int m_bpr;                // 128-row blocks per rank shard (fused modes)
   int b_half_rows;          // SwiGLU: row offset of the "up" half inside B; plain: unused
   const uint32_t* a_ready;  // optional arrival flags per 128-row block (local memory)
@@ -168,6 +167,13 @@ __device__ __forceinline__ int order_rows(const Args& a, int m, int tiles_rows, 
     const int bpr = a.m_bpr / unit, n = a.comm.nranks, r = a.comm.rank;
     if (m < bpr) return r * bpr + m;
     const int i = m - bpr, j = i / (n - 1), q = i % (n - 1) + 1;
+    return ((r + q) % n) * bpr + j;
+  }
+  if (a.m_order == 3) {
+    // all-gather by copy-engine lanes: my own shard, then the whole shard of rank r+1, r+2, ...
+    const int bpr = a.m_bpr / unit, n = a.comm.nranks, r = a.comm.rank;
+    if (m < bpr) return r * bpr + m;
+    const int i = m - bpr, q = i / bpr + 1, j = i - (q - 1) * bpr;
     return ((r + q) % n) * bpr + j;
   }
   if (a.m_order == 2) {
@@ -572,7 +578,7 @@ __device__ __forceinline__ void epilogue_tile(const Args& a, const PeerMaps& pm,
       ptx::tmem_ld_wait();
       uint8_t* buf = stage + (stage_it % NBUF) * EPI_BUF_BYTES;
       ++stage_it;
-      if (lane == 0 && !a.comm.rs_plain_stores) ptx::tma_store_wait_read<NBUF - 1>();  // the store that last used this buffer has read it
+      if (lane == 0) ptx::tma_store_wait_read<NBUF - 1>();  // the store that last used this buffer has read it
       __syncwarp();
       uint8_t* myrow = buf + lane * 128;
 #pragma unroll
@@ -586,24 +592,6 @@ __device__ __forceinline__ void epilogue_tile(const Args& a, const PeerMaps& pm,
         *reinterpret_cast<uint4*>(myrow + ((k ^ (lane & 7)) << 4)) = v;  // 128-byte swizzle
       }
       const int col0 = nb * BN + g * 64;
-      if (a.comm.rs_plain_stores) {
-        // plain stores: four rows x 128 contiguous bytes per warp instruction, posted writes that
-        // do not occupy the TMA unit
-        __syncwarp();
-        if (col0 + 64 <= a.N && !(a.debug & 2)) {
-          char* dbase = a.comm.stage_peer[(a.debug & 16) ? a.comm.rank : owner] +
-                        (static_cast<size_t>(drow) * a.N + col0) * 2;
-          const int cch = lane & 7;
-#pragma unroll
-          for (int it = 0; it < 8; ++it) {
-            const int rr = (lane >> 3) + 4 * it;
-            const uint4 v = *reinterpret_cast<const uint4*>(buf + rr * 128 + ((cch ^ (rr & 7)) << 4));
-            ptx::st_global_v4(dbase + static_cast<size_t>(rr) * a.N * 2 + (cch << 4), v);
-          }
-        }
-        __syncwarp();  // the buffer may be rewritten
-        continue;
-      }
       ptx::fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0 && col0 < a.N && !(a.debug & 2)) {
@@ -680,12 +668,8 @@ __device__ __forceinline__ void epilogue_tile(const Args& a, const PeerMaps& pm,
 // the MMA warp needs all four to have drained accumulator t-2 before it can produce tile t.
 template <int PENDING>
 __device__ __forceinline__ void publish_tile(const Args& a, int mb, int lane, uint32_t* counter) {
-  if (a.comm.rs_plain_stores) {
-    ptx::fence_sys();  // every lane's own stores have been performed
-    __syncwarp();
-  }
   if (lane != 0) return;
-  if (!a.comm.rs_plain_stores) ptx::tma_store_wait<PENDING>();
+  ptx::tma_store_wait<PENDING>();
   __threadfence_block();
   const uint32_t old = atomicAdd(counter, 1u);
   if ((old & 3u) == 3u) {

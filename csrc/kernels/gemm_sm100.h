@@ -33,6 +33,7 @@ struct GemmFusion {
   const void* a_shard = nullptr;
   int a_inplace = 0;
   int a_external = 0;  // the rows arrive by copy engines: no communication CTAs, flags are set to 1
+  int a_peer_major = 0;  // visit the other ranks' shards one rank after the other, nearest first (copy-engine lanes)
   int a_spread = 0;    // no communication CTAs either: a forwarder warp in every GEMM CTA pushes the shard
   void* a_full_peer[UCCL_MAX_LOCAL_RANKS] = {};
   uint32_t* ready_peer[UCCL_MAX_LOCAL_RANKS] = {};

@@ -278,7 +278,9 @@ ucclResult_t ucclCommSetBlocks(ucclComm_t comm, int blocks);
 /* Options of the fused all-gather -> GEMM on this communicator; 0 keeps the default of a field.
  * agMode: 1 = copy engines move the rows, 2 = communication CTAs inside the GEMM launch,
  *         3 = a forwarder warp in every GEMM CTA ("spread").
- * commCtas: number of those CTAs (mode 2).  ceChunks: copies per peer (mode 1).
+ * commCtas: number of those CTAs (mode 2); in mode 1 the number of copy-engine lanes (0 = one stream
+ * per peer, k = k streams that serve the peers one after the other, nearest first).
+ * ceChunks: copies per peer (mode 1).
  * The environment variables UCCL_FUSED_AG / UCCL_FUSED_COMM_CTAS / UCCL_FUSED_CE_CHUNKS win. */
 ucclResult_t ucclCommSetFusedOptions(ucclComm_t comm, int agMode, int commCtas, int ceChunks);
 

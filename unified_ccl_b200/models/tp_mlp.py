@@ -47,8 +47,9 @@ class TensorParallelMLP:
 
     __call__ = forward
 
-    # candidates of autotune(): (all-gather mode, communication CTAs, copy-engine chunks per peer)
-    AG_CANDIDATES = (("spread", 0, 0), ("ce", 0, 1), ("ce", 0, 2), ("ce", 0, 4), ("kernel", 8, 0), ("kernel", 16, 0), ("kernel", 24, 0))
+    # candidates of autotune(): (all-gather mode, communication CTAs or copy-engine lanes, chunks per peer)
+    AG_CANDIDATES = (("ce", 0, 1), ("ce", 0, 2), ("ce", 0, 4), ("ce", 1, 2), ("ce", 2, 2), ("ce", 2, 4), ("ce", 3, 2),
+                     ("spread", 0, 0), ("kernel", 8, 0), ("kernel", 16, 0), ("kernel", 24, 0))
 
     def autotune(self, x_shard: torch.Tensor, iters: int = 3, candidates=None):
         """Times the all-gather -> GEMM half of the block under each candidate setting (CUDA events,
@@ -57,6 +58,8 @@ class TensorParallelMLP:
         if self.tp == 1:
             return {}
         cands = tuple(candidates or self.AG_CANDIDATES)
+        if self.tp <= 2:  # lanes only differ from one stream per peer when there are several peers
+            cands = tuple(c for c in cands if not (c[0] == "ce" and c[1] > 0))
         times = torch.zeros(len(cands), device=self.h.device, dtype=torch.float32)
         stream = torch.cuda.current_stream(self.h.device)
         for i, (mode, ctas, chunks) in enumerate(cands):
