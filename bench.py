@@ -72,6 +72,7 @@ def main():
     mlp = TensorParallelMLP(comm, HIDDEN, FFN, tokens, seed=0)
     base = NcclCublasMLP(mlp.w_gate_up, mlp.w_down, tokens, world)
     autotune = {}
+    autotune_rs = {}
     g = torch.Generator(device="cpu").manual_seed(1234 + rank)
     x_host = torch.randn(rows, HIDDEN, generator=g).to(torch.bfloat16).pin_memory()
     x_dev = x_host.to(dev)
@@ -79,6 +80,10 @@ def main():
     if world > 1 and not os.environ.get("UCCL_FUSED_AG"):
         autotune = {"%s/ctas%d/chunks%d" % k: v for k, v in mlp.autotune(x_dev).items()}
         autotune["chosen"] = "%s/ctas%d/chunks%d" % mlp.ag_choice
+    if world > 1 and not os.environ.get("UCCL_FUSED_RS"):
+        mlp(x_dev)  # fills the activations the second half works on
+        autotune_rs = {"%s/chunks%d" % k: v for k, v in mlp.autotune_rs().items()}
+        autotune_rs["chosen"] = "%s/chunks%d" % mlp.rs_choice
 
     def barrier():
         if world > 1:
@@ -198,6 +203,7 @@ def main():
             "allreduce_vs_nccl": sweep,
             "comm": {k: comm.info[k] for k in ("nvls", "p2p_mode", "net_active")},
             "ag_gemm_autotune_us": autotune,
+            "gemm_rs_autotune_us": autotune_rs,
             "halves": halves,
         }
         print(json.dumps(out))

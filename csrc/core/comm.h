@@ -97,6 +97,11 @@ struct Comm {
   cudaEvent_t ceEvent[UCCL_MAX_LOCAL_RANKS] = {};
   cudaEvent_t ceStart = nullptr;
   bool ceReady = false;
+  // reduce-scatter by copy engines: local send buffer (grown on demand) and chunk counters / flags
+  void* rsSendBuf = nullptr;
+  size_t rsSendBytes = 0;
+  void* rsCtl = nullptr;              // u32 counts at +0, u64 flags at +1024
+  int fusedRsMode = 0, fusedRsChunks = 0;  // ucclCommSetFusedRsOptions (0 = default)
   void* onesDev = nullptr;            // 32-bit ones at the GEMM flag stride (source of copy-engine flag writes)
 
   // network path

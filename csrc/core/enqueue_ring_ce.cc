@@ -19,6 +19,7 @@
 
 #include "../kernels/coll_device_types.h"
 #include "../kernels/collectives.cuh"
+#include "cuda_driver.h"
 #include "enqueue.h"
 #include "log.h"
 
@@ -88,6 +89,16 @@ ucclResult_t sideCopyBegin(Comm* c, void* dst, const void* src, size_t bytes, cu
 // which the GEMM then visits them - instead of all of them at the very end.
 // Call allGatherPushEnd after the kernel launch.
 namespace {
+// a column of 32-bit ones at the flag stride, the source of every copy-engine flag write
+ucclResult_t ensureOnes(Comm* c) {
+  if (c->onesDev) return ucclSuccess;
+  if (cudaMalloc(&c->onesDev, kGemmFlagStrideBytes * kGemmMaxRowBlocks) != cudaSuccess) return cudaFail(c, "cudaMalloc");
+  if (cudaMemset(c->onesDev, 0, kGemmFlagStrideBytes * kGemmMaxRowBlocks) != cudaSuccess ||
+      cudaMemset2D(c->onesDev, kGemmFlagStrideBytes, 1, 1, kGemmMaxRowBlocks) != cudaSuccess)
+    return cudaFail(c, "cudaMemset2D");
+  return ucclSuccess;
+}
+
 int cePushStreams(Comm* c, int lanes, bool copyOwn, cudaStream_t* out) {
   const int n = c->localRanks, me = c->localRank;
   int k = 0;
@@ -109,13 +120,8 @@ ucclResult_t allGatherPushBegin(Comm* c, const void* shard, char* const* fullPee
   const ucclResult_t r = ensureCeStreams(c);
   if (r != ucclSuccess) return r;
   const int n = c->localRanks, me = c->localRank;
-  if (!c->onesDev) {
-    // a column of 32-bit ones at the flag stride, the source of every flag copy
-    if (cudaMalloc(&c->onesDev, kGemmFlagStrideBytes * kGemmMaxRowBlocks) != cudaSuccess) return cudaFail(c, "cudaMalloc");
-    if (cudaMemset(c->onesDev, 0, kGemmFlagStrideBytes * kGemmMaxRowBlocks) != cudaSuccess ||
-        cudaMemset2D(c->onesDev, kGemmFlagStrideBytes, 1, 1, kGemmMaxRowBlocks) != cudaSuccess)
-      return cudaFail(c, "cudaMemset2D");
-  }
+  const ucclResult_t ro = ensureOnes(c);
+  if (ro != ucclSuccess) return ro;
   cudaStream_t streams[UCCL_MAX_LOCAL_RANKS + 1];
   const int nstreams = cePushStreams(c, lanes, copyOwn, streams);
   if (cudaEventRecord(c->ceStart, s) != cudaSuccess) return cudaFail(c, "cudaEventRecord");
@@ -170,6 +176,60 @@ ucclResult_t allGatherPushEnd(Comm* c, bool copyOwn, int lanes, cudaStream_t s) 
     // one event per stream: the events array has an entry for every local rank
     if (cudaEventRecord(c->ceEvent[i], streams[i]) != cudaSuccess) return cudaFail(c, "cudaEventRecord");
     if (cudaStreamWaitEvent(s, c->ceEvent[i], 0) != cudaSuccess) return cudaFail(c, "cudaStreamWaitEvent");
+  }
+  return ucclSuccess;
+}
+
+// GEMM -> reduce-scatter by copy engines.  The kernel launched on `s` writes its partial results
+// for rank o into sendBuf[o] and raises slabFlag[q * chunks + ch] (q = position of o in the order
+// me+1, me+2, ...) when chunk ch of that slab is complete.  One side stream per peer waits for each
+// flag (a stream memory operation), copies the chunk into slot [me] of the peer's staging buffer
+// and then a one onto the peer's arrival flag [me][ch].
+ucclResult_t reduceScatterPushBegin(Comm* c, const char* sendBuf, char* const* stagePeer, char* const* ceDonePeer,
+                                    unsigned long long* slabFlag, size_t slabBytes, int chunks, cudaStream_t s) {
+  ucclResult_t r = ensureCeStreams(c);
+  if (r != ucclSuccess) return r;
+  if ((r = ensureOnes(c)) != ucclSuccess) return r;
+  const DriverApi& d = driverApi();
+  if (!d.ok || !d.streamWaitValue64) {
+    commSetError(c, "stream memory operations are not available");
+    return ucclInvalidUsage;
+  }
+  const int n = c->localRanks, me = c->localRank;
+  const size_t chunkBytes = slabBytes / chunks;
+  if (cudaEventRecord(c->ceStart, s) != cudaSuccess) return cudaFail(c, "cudaEventRecord");
+  for (int q = 0; q + 1 < n; ++q) {
+    const int o = (me + 1 + q) % n;
+    cudaStream_t st = c->ceStream[o];
+    if (cudaStreamWaitEvent(st, c->ceStart, 0) != cudaSuccess) return cudaFail(c, "cudaStreamWaitEvent");
+    for (int ch = 0; ch < chunks; ++ch) {
+      const CUresult w = d.streamWaitValue64(reinterpret_cast<CUstream>(st),
+                                             reinterpret_cast<CUdeviceptr>(slabFlag + q * chunks + ch), 1,
+                                             CU_STREAM_WAIT_VALUE_GEQ);
+      if (w != CUDA_SUCCESS) {
+        commSetError(c, "cuStreamWaitValue64: %s", driverErrorString(w));
+        return ucclSystemError;
+      }
+      if (cudaMemcpyAsync(stagePeer[o] + static_cast<size_t>(me) * slabBytes + ch * chunkBytes,
+                          sendBuf + static_cast<size_t>(o) * slabBytes + ch * chunkBytes, chunkBytes,
+                          cudaMemcpyDeviceToDevice, st) != cudaSuccess)
+        return cudaFail(c, "cudaMemcpyAsync");
+      if (cudaMemcpyAsync(ceDonePeer[o] + static_cast<size_t>(me * chunks + ch) * kGemmFlagStrideBytes, c->onesDev,
+                          kGemmFlagStrideBytes, cudaMemcpyDeviceToDevice, st) != cudaSuccess)
+        return cudaFail(c, "cudaMemcpyAsync");
+    }
+  }
+  return ucclSuccess;
+}
+// After the kernel launch: once the kernel has ended - normally or not - every flag is raised so
+// that no side stream can be left waiting, then `s` waits for the side streams.
+ucclResult_t reduceScatterPushEnd(Comm* c, unsigned long long* slabFlag, int nflags, cudaStream_t s) {
+  if (cudaMemsetAsync(slabFlag, 0xff, sizeof(unsigned long long) * nflags, s) != cudaSuccess) return cudaFail(c, "cudaMemsetAsync");
+  const int n = c->localRanks, me = c->localRank;
+  for (int p = 0; p < n; ++p) {
+    if (p == me) continue;
+    if (cudaEventRecord(c->ceEvent[p], c->ceStream[p]) != cudaSuccess) return cudaFail(c, "cudaEventRecord");
+    if (cudaStreamWaitEvent(s, c->ceEvent[p], 0) != cudaSuccess) return cudaFail(c, "cudaStreamWaitEvent");
   }
   return ucclSuccess;
 }

@@ -75,6 +75,29 @@ int fusedAgMode(Comm* c) {
   return 1;
 }
 
+// Chunks per slab when the GEMM -> reduce-scatter fusion should use copy engines, 0 when the
+// epilogue should store to the owners itself.  UCCL_FUSED_RS=ce|kernel and UCCL_FUSED_RS_CHUNKS win
+// over ucclCommSetFusedRsOptions; the copy-engine form needs CTA pairs (rows per rank a multiple of
+// 256) and a chunk count that divides the row blocks of a rank.
+int fusedRsCeChunks(Comm* c, int blocksPerRank) {
+  int mode = c->fusedRsMode, chunks = c->fusedRsChunks;
+  if (const char* s = getenv("UCCL_FUSED_RS")) {
+    if (!strcasecmp(s, "ce") || !strcasecmp(s, "copy_engine")) mode = 2;
+    else if (!strcasecmp(s, "kernel")) mode = 1;
+  }
+  if (const char* s = getenv("UCCL_FUSED_RS_CHUNKS")) {
+    if (atoi(s) > 0) chunks = atoi(s);
+  }
+  if (mode != 2 || c->localRanks < 2 || blocksPerRank % 2 != 0) return 0;
+  if (const char* s = getenv("UCCL_GEMM_PAIR")) {
+    if (*s && atoi(s) == 0) return 0;
+  }
+  if (chunks <= 0) chunks = 4;
+  chunks = std::min(std::min(chunks, kGemmMaxCeChunks), blocksPerRank / 2);
+  while (chunks > 1 && (blocksPerRank % chunks != 0 || (blocksPerRank / chunks) % 2 != 0)) --chunks;
+  return std::max(chunks, 1);
+}
+
 // UCCL_FUSED_SELF=1 runs the fused kernels on a one-rank communicator too (every "peer" is this
 // GPU): the whole data path of the fusion in a single process, for profiling one kernel alone.
 bool fusedSelf() {
@@ -307,6 +330,59 @@ extern "C" ucclResult_t ucclGemmReduceScatter(const void* A, const void* W, void
   // this launch's remote writes after every rank's previous use of its staging buffer.
   uint32_t* done = reinterpret_cast<uint32_t*>(c->arena->local + kArenaGemmDoneOff);
   if (cudaMemsetAsync(done, 0, kGemmFlagStrideBytes * (M / 128), s) != cudaSuccess) return ucclSystemError;
+  const int rsChunks = fusedRsCeChunks(c, M / n / 128);
+  if (rsChunks > 0) {
+    // ---- copy engines carry the slabs (see reduceScatterPushBegin)
+    const size_t slabBytes = static_cast<size_t>(M / n) * N * 2;
+    const size_t need = static_cast<size_t>(M) * N * 2;
+    if (c->rsSendBytes < need) {
+      if (cudaStreamSynchronize(s) != cudaSuccess) return ucclSystemError;  // an earlier launch may still use the old buffer
+      if (c->rsSendBuf) cudaFree(c->rsSendBuf);
+      c->rsSendBuf = nullptr;
+      c->rsSendBytes = 0;
+      if (cudaMalloc(&c->rsSendBuf, need) != cudaSuccess) {
+        commSetError(c, "out of memory for the %zu-byte reduce-scatter send buffer", need);
+        return ucclSystemError;
+      }
+      c->rsSendBytes = need;
+    }
+    if (!c->rsCtl && cudaMalloc(&c->rsCtl, 4096) != cudaSuccess) return ucclSystemError;
+    uint32_t* slabCount = static_cast<uint32_t*>(c->rsCtl);
+    unsigned long long* slabFlag = reinterpret_cast<unsigned long long*>(static_cast<char*>(c->rsCtl) + 1024);
+    char* ceDone = c->arena->local + kArenaGemmCeDoneOff;
+    if (cudaMemsetAsync(c->rsCtl, 0, 4096, s) != cudaSuccess ||
+        cudaMemsetAsync(ceDone, 0, kGemmFlagStrideBytes * n * rsChunks, s) != cudaSuccess)
+      return ucclSystemError;
+    if ((r = enqueueBarrier(c, s)) != ucclSuccess) return r;
+    GemmFusion f;
+    f.role = 3;
+    f.rank = c->localRank;
+    f.nranks = n;
+    f.timeout_ns = c->dev.timeoutNs;
+    f.abort_flag = c->dev.abortFlag;
+    f.rows_per_rank = M / n;
+    char* stagePeer[UCCL_MAX_LOCAL_RANKS];
+    char* ceDonePeer[UCCL_MAX_LOCAL_RANKS];
+    for (int p = 0; p < n; ++p) {
+      f.stage_peer[p] = stagePeer[p] = sp.seg->peer[p] + sp.off;
+      f.done_peer[p] = reinterpret_cast<uint32_t*>(c->arena->peer[p] + kArenaGemmDoneOff);
+      ceDonePeer[p] = c->arena->peer[p] + kArenaGemmCeDoneOff;
+    }
+    f.done_peer[c->localRank] = done;
+    f.slab_count = slabCount;
+    f.slab_flag = slabFlag;
+    f.ce_done = reinterpret_cast<const uint32_t*>(ceDone);
+    f.ce_chunks = rsChunks;
+    f.rs_out = out;
+    f.rs_ldo = N;
+    g.C = c->rsSendBuf;
+    commCount(c, ucclCollReduceScatter, static_cast<size_t>(M) * N * 2, ucclAlgoCopyEngine);
+    if ((r = reduceScatterPushBegin(c, static_cast<const char*>(c->rsSendBuf), stagePeer, ceDonePeer, slabFlag, slabBytes,
+                                    rsChunks, s)) != ucclSuccess)
+      return r;
+    if ((r = launchGemmBf16(g, &f, s)) != ucclSuccess) return r;
+    return reduceScatterPushEnd(c, slabFlag, (n - 1) * rsChunks, s);
+  }
   if ((r = enqueueBarrier(c, s)) != ucclSuccess) return r;
   GemmFusion f;
   f.role = 2;

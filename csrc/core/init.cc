@@ -15,6 +15,7 @@
 
 #include "../rma/rma.h"
 #include "comm.h"
+#include "../kernels/device_comm.h"
 #include "../transport/net_plugin.h"
 #include "cuda_driver.h"
 #include "log.h"
@@ -366,6 +367,8 @@ void destroyComm(Comm* c) {
     }
     if (c->ceStart) cudaEventDestroy(c->ceStart);
     if (c->onesDev) cudaFree(c->onesDev);
+    if (c->rsSendBuf) cudaFree(c->rsSendBuf);
+    if (c->rsCtl) cudaFree(c->rsCtl);
     if (c->epochsDev) cudaFree(c->epochsDev);
     if (c->hostFlags) cudaFreeHost(c->hostFlags);
     traceDump(c);
@@ -564,6 +567,15 @@ extern "C" ucclResult_t ucclCommSetFusedOptions(ucclComm_t comm, int agMode, int
   c->fusedAgMode = agMode;
   c->fusedCommCtas = commCtas;
   c->fusedCeChunks = ceChunks;
+  return ucclSuccess;
+}
+
+extern "C" ucclResult_t ucclCommSetFusedRsOptions(ucclComm_t comm, int rsMode, int ceChunks) {
+  Comm* c = toComm(comm);
+  if (!commValid(c)) return ucclInvalidArgument;
+  if (rsMode < 0 || rsMode > 2 || ceChunks < 0 || ceChunks > kGemmMaxCeChunks) return ucclInvalidArgument;
+  c->fusedRsMode = rsMode;
+  c->fusedRsChunks = ceChunks;
   return ucclSuccess;
 }
 

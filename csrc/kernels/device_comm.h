@@ -19,9 +19,11 @@ constexpr size_t kP2pSlotBytes = 2u << 20;
 constexpr size_t kArenaBarrierOff = 0;                 // u32 [kMaxBlocks][UCCL_MAX_LOCAL_RANKS]
 // fused GEMM flags: one 128-byte line per 128-row block (see FLAG_STRIDE in gemm_sm100.cuh)
 constexpr size_t kGemmFlagStrideBytes = 128;
-constexpr int kGemmMaxRowBlocks = 2048;
-constexpr size_t kArenaGemmReadyOff = 512u << 10;      // all-gather arrival counters, 256 KiB
-constexpr size_t kArenaGemmDoneOff = 768u << 10;       // reduce-scatter counters, 256 KiB
+constexpr int kGemmMaxRowBlocks = 1024;
+constexpr int kGemmMaxCeChunks = 8;
+constexpr size_t kArenaGemmReadyOff = 512u << 10;      // all-gather arrival counters, 128 KiB
+constexpr size_t kArenaGemmCeDoneOff = 640u << 10;     // reduce-scatter by copy engines: [rank][chunk] arrival flags, 16 KiB
+constexpr size_t kArenaGemmDoneOff = 768u << 10;       // reduce-scatter counters, 128 KiB
 constexpr size_t kArenaP2pCtrlOff = 96u << 10;         // P2pCtrl [UCCL_MAX_LOCAL_RANKS][kP2pStripes]
 constexpr size_t kArenaMoeCtrlOff = 128u << 10;        // MoE counters (see moe.cu)
 constexpr size_t kArenaLLOff = 1u << 20;               // [2][kLLBlocks][UCCL_MAX_LOCAL_RANKS][kLLSlotBytes]

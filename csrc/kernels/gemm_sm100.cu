@@ -133,7 +133,8 @@ ucclResult_t launchGemmBf16(const GemmLaunch& g, const GemmFusion* f, cudaStream
     return ucclInvalidArgument;
   if (g.epilogue == gemm::kEpiSwiGLU && (g.N % 2 != 0)) return ucclInvalidArgument;
   const int role = f ? f->role : 0;
-  if (role == gemm::kCommReduceScatter && g.epilogue != gemm::kEpiStore) return ucclInvalidArgument;
+  if ((role == gemm::kCommReduceScatter || role == gemm::kCommReduceScatterCe) && g.epilogue != gemm::kEpiStore)
+    return ucclInvalidArgument;
 
   CUtensorMap tmA, tmB;
   if (!makeTensorMap(&tmA, g.A, g.M, g.K, g.lda, gemm::BK, gemm::BM)) return ucclSystemError;
@@ -201,6 +202,22 @@ ucclResult_t launchGemmBf16(const GemmLaunch& g, const GemmFusion* f, cudaStream
         if (!makeTensorMap(&pm.m[0], f->a_shard, f->rows_per_rank, g.K, g.K, gemm::BK, gemm::BM)) return ucclSystemError;
       }
       a.m_order = (a.debug & 4) ? 0 : (f->a_peer_major ? 3 : 1);
+    } else if (role == gemm::kCommReduceScatterCe) {
+      // copy engines carry the slabs: the kernel only writes local memory and counts
+      if (!usePairKernel() || f->rows_per_rank % (2 * gemm::BM) != 0 || f->ce_chunks < 1 ||
+          blk_per_rank % f->ce_chunks != 0 || (blk_per_rank / f->ce_chunks) % 2 != 0 || g.ldc != g.N)
+        return ucclInvalidArgument;
+      c.done_peer[f->rank] = f->done_peer[f->rank];
+      c.stage_local = static_cast<const char*>(f->stage_peer[f->rank]);
+      c.slab_count = f->slab_count;
+      c.slab_flag = f->slab_flag;
+      c.ce_done = f->ce_done;
+      c.ce_chunks = f->ce_chunks;
+      c.slab_target = static_cast<uint32_t>((blk_per_rank / f->ce_chunks) * a.tiles_n * 4);
+      c.own_target = static_cast<uint32_t>(a.tiles_n * 4);
+      c.rs_out = static_cast<char*>(f->rs_out);
+      c.rs_ldo = f->rs_ldo;
+      a.m_order = 4;
     } else {
       for (int i = 0; i < f->nranks; ++i) {
         c.done_peer[i] = f->done_peer[i];
@@ -238,6 +255,7 @@ ucclResult_t launchGemmBf16(const GemmLaunch& g, const GemmFusion* f, cudaStream
     } else {
       if (role == gemm::kCommAllGather) e = launchPairT<gemm::kEpiStore, gemm::kCommAllGather>(tmA, tmB, pm, a, grid, stream);
       else if (role == gemm::kCommReduceScatter) e = launchPairT<gemm::kEpiStore, gemm::kCommReduceScatter>(tmA, tmB, pm, a, grid, stream);
+      else if (role == gemm::kCommReduceScatterCe) e = launchPairT<gemm::kEpiStore, gemm::kCommReduceScatterCe>(tmA, tmB, pm, a, grid, stream);
       else e = launchPairT<gemm::kEpiStore, gemm::kCommNone>(tmA, tmB, pm, a, grid, stream);
     }
   } else {

@@ -74,7 +74,12 @@ enum Epilogue : int {
   kEpiStore = 0,   // C[M,N] bf16
   kEpiSwiGLU = 1,  // B rows of a tile are [128 gate rows | 128 up rows]; C[M,N/2] = silu(g)*u
 };
-enum CommRole : int { kCommNone = 0, kCommAllGather = 1, kCommReduceScatter = 2 };
+enum CommRole : int {
+  kCommNone = 0,
+  kCommAllGather = 1,
+  kCommReduceScatter = 2,    // epilogue TMA-stores tiles into the owners' staging slots
+  kCommReduceScatterCe = 3,  // epilogue stores locally, copy engines carry finished slabs to their owners
+};
 
 constexpr int kMaxPeers = 16;
 // Cross-rank flags and counters are one per 128-byte line: hundreds of waiting CTAs poll them,
@@ -96,6 +101,15 @@ struct CommArgs {
   // reduce-scatter: every rank owns a staging buffer [nranks][rows_per_rank][N]; slot s receives
   // rank s's partial result for the owner's rows (tensor maps in PeerMaps)
   const char* stage_local = nullptr;
+  // copy-engine variant: partial tiles for other ranks go to a local send buffer (Args.C); per
+  // chunk of a slab a counter of finished (warp, tile) pairs and a 64-bit flag that a side
+  // stream waits on; per (source rank, chunk) an arrival flag that the source's copy engine sets
+  uint32_t* slab_count = nullptr;             // local [(nranks - 1) * ce_chunks]
+  unsigned long long* slab_flag = nullptr;    // local [(nranks - 1) * ce_chunks]
+  const uint32_t* ce_done = nullptr;          // local, FLAG_STRIDE apart: [nranks * ce_chunks]
+  int ce_chunks = 1;                          // chunks per slab; divides the row blocks per rank
+  uint32_t slab_target = 0;                   // (warp, tile) pairs per chunk
+  uint32_t own_target = 0;                    // (warp, tile) pairs per own row block
   uint32_t* done_peer[kMaxPeers] = {};  // every rank's per-row-block counters, zero at launch
   uint32_t done_target = 0;             // nranks * column tiles
   char* rs_out = nullptr;               // [rows_per_rank, N] bf16
@@ -117,7 +131,7 @@ struct Args {
   int comm_ctas;            // CTAs [0, comm_ctas) run the communication role (scheduled first)
   int m_rot;                // row-block rotation: logical block i maps to (i + m_rot) % tiles_m
   int m_order;              // 0: rotation only; 1: all-gather order; 2: reduce-scatter order;
-                            // 3: all-gather, one peer after the other
+                            // 3: all-gather, one peer after the other; 4: reduce-scatter, slab by slab
   int m_bpr;                // 128-row blocks per rank shard (fused modes)
   int b_half_rows;          // SwiGLU: row offset of the "up" half inside B; plain: unused
   const uint32_t* a_ready;  // optional arrival flags per 128-row block (local memory)
@@ -168,6 +182,13 @@ __device__ __forceinline__ int order_rows(const Args& a, int m, int tiles_rows, 
     if (m < bpr) return r * bpr + m;
     const int i = m - bpr, j = i / (n - 1), q = i % (n - 1) + 1;
     return ((r + q) % n) * bpr + j;
+  }
+  if (a.m_order == 4) {
+    // reduce-scatter by copy engines: the slab of rank r+1 first, then r+2, ..., my own last, so
+    // that finished slabs travel while the later ones are computed
+    const int bpr = a.m_bpr / unit, n = a.comm.nranks, r = a.comm.rank;
+    const int q = m / bpr, j = m - q * bpr;
+    return ((r + 1 + q) % n) * bpr + j;
   }
   if (a.m_order == 3) {
     // all-gather by copy-engine lanes: my own shard, then the whole shard of rank r+1, r+2, ...
@@ -464,7 +485,7 @@ __device__ __forceinline__ void tail_sum_piece(const uint8_t* sbase, uint32_t P,
 // from shared memory and write the bf16 result.  192 KiB of loads in flight per SM without
 // holding them in registers.
 __device__ void reduce_scatter_tail(const Args& a, uint8_t* smem, uint64_t* tbars, volatile uint32_t* bail, int cta,
-                                    int nctas) {
+                                    int nctas, bool ce) {
   const CommArgs& c = a.comm;
   const int n = c.nranks, bpr = a.m_bpr;
   constexpr int TSTAGES = 3;
@@ -492,10 +513,35 @@ __device__ void reduce_scatter_tail(const Args& a, uint8_t* smem, uint64_t* tbar
     for (int i = 0; i < TSTAGES; ++i) ptx::mbar_init(&tbars[i], 1);
     ptx::mbar_fence_init();
   }
-  // every thread looks at one counter; the loader takes the complete prefix
+  // Row block b of mine is complete when, TMA variant: its counter has every rank's tiles;
+  // copy-engine variant: my own tiles are counted and every other rank's copy engine has set the
+  // flag of the chunk that holds the block.
+  const uint32_t ownTarget = ce ? c.own_target : c.done_target;
+  const int blocksPerChunk = ce ? bpr / c.ce_chunks : 1;
+  auto peek = [&](int b) -> bool {
+    if (ptx::ld_relaxed_sys_u32(done + static_cast<size_t>(b) * FLAG_STRIDE) < ownTarget) return false;
+    if (ce) {
+      const int ch = b / blocksPerChunk;
+      for (int p = 0; p < n; ++p)
+        if (p != c.rank && ptx::ld_relaxed_sys_u32(c.ce_done + static_cast<size_t>(p * c.ce_chunks + ch) * FLAG_STRIDE) < 1u)
+          return false;
+    }
+    return true;
+  };
+  auto await = [&](int b) -> bool {  // bounded; thread 0 only
+    if (!wait_flag_geq(done + static_cast<size_t>(b) * FLAG_STRIDE, ownTarget, c.timeout_ns, c.abort_flag)) return false;
+    if (ce) {
+      const int ch = b / blocksPerChunk;
+      for (int p = 0; p < n; ++p)
+        if (p != c.rank && !wait_flag_geq(c.ce_done + static_cast<size_t>(p * c.ce_chunks + ch) * FLAG_STRIDE, 1u,
+                                          c.timeout_ns, c.abort_flag))
+          return false;
+    }
+    return true;
+  };
+  // every thread looks at one row block; the loader takes the complete prefix
   uint32_t* s_ready = reinterpret_cast<uint32_t*>(smem);  // [bpr] flags, shared memory is idle here
-  for (int b = threadIdx.x; b < bpr; b += blockDim.x)
-    s_ready[b] = ptx::ld_relaxed_sys_u32(done + static_cast<size_t>(b) * FLAG_STRIDE) >= c.done_target ? 1u : 0u;
+  for (int b = threadIdx.x; b < bpr; b += blockDim.x) s_ready[b] = peek(b) ? 1u : 0u;
   __syncthreads();
   if (threadIdx.x == 0) {
     while (readyUpTo < bpr && s_ready[readyUpTo]) ++readyUpTo;
@@ -507,7 +553,7 @@ __device__ void reduce_scatter_tail(const Args& a, uint8_t* smem, uint64_t* tbar
     const int u = cta + i * nctas;
     const int b = u / pieces, part = u - b * pieces;
     if (b >= readyUpTo) {
-      if (!wait_flag_geq(done + static_cast<size_t>(b) * FLAG_STRIDE, c.done_target, c.timeout_ns, c.abort_flag)) {
+      if (!await(b)) {
         if (a.err) atomicCAS(a.err, 0u, 0x52530000u | static_cast<uint32_t>(b));
         *bail = 1;
         return;
@@ -562,7 +608,7 @@ __device__ void reduce_scatter_tail(const Args& a, uint8_t* smem, uint64_t* tbar
 // `taddr` addresses this warp's 32 TMEM lanes of the accumulator; `mb` is the 128-row block.
 template <int EPI, int COMM, int NBUF>
 __device__ __forceinline__ void epilogue_tile(const Args& a, const PeerMaps& pm, uint32_t taddr, int mb, int nb, int q,
-                                              int lane, uint8_t* stage, uint32_t& stage_it) {
+                                              int lane, uint8_t* stage, uint32_t& stage_it, __nv_bfloat16* cbase) {
   const int row = mb * BM + q * 32 + lane;
   if (COMM == kCommReduceScatter) {
     // bf16 tile -> swizzled shared memory -> TMA store into the owner's staging slot [my rank]
@@ -602,7 +648,7 @@ __device__ __forceinline__ void epilogue_tile(const Args& a, const PeerMaps& pm,
     return;  // the caller publishes the tile once these groups have completed
   }
   if (EPI == kEpiStore) {
-    __nv_bfloat16* crow = a.C + static_cast<size_t>(row) * a.ldc + static_cast<size_t>(nb) * BN;
+    __nv_bfloat16* crow = cbase + static_cast<size_t>(row) * a.ldc + static_cast<size_t>(nb) * BN;
 #pragma unroll 1
     for (int c = 0; c < BN / 32; ++c) {
       uint32_t r[32];
@@ -629,7 +675,7 @@ __device__ __forceinline__ void epilogue_tile(const Args& a, const PeerMaps& pm,
   } else {
     // gate columns [0,128) and up columns [128,256) of the accumulator
     const int out_n = a.N / 2;
-    __nv_bfloat16* crow = a.C + static_cast<size_t>(row) * a.ldc + static_cast<size_t>(nb) * (BN / 2);
+    __nv_bfloat16* crow = cbase + static_cast<size_t>(row) * a.ldc + static_cast<size_t>(nb) * (BN / 2);
 #pragma unroll 1
     for (int c = 0; c < BN / 64; ++c) {
       uint32_t g[32], u[32];
@@ -820,7 +866,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (!ptx::mbar_wait_bounded(&tfull_bar[acc], acc_ph, bail)) break;
       ptx::tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
-      epilogue_tile<EPI, COMM, 2>(a, pm, taddr, mb, nb, q, lane, stage, stage_it);
+      epilogue_tile<EPI, COMM, 2>(a, pm, taddr, mb, nb, q, lane, stage, stage_it, a.C);
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&tempty_bar[acc]);
@@ -843,7 +889,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (a.times && cta_id == 0 && threadIdx.x == 0) a.times[1] = ptx::globaltimer_ns();
   if (COMM == kCommReduceScatter && !*bail && !(a.debug & 1)) {
     if (a.debug & 128) reduce_scatter_tail_direct(a, cta_id, gemm_ctas);
-    else reduce_scatter_tail(a, smem, bars + 24, bail, cta_id, gemm_ctas);
+    else reduce_scatter_tail(a, smem, bars + 24, bail, cta_id, gemm_ctas, false);
   }
 }
 
@@ -1009,10 +1055,39 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       if (!ptx::mbar_wait_bounded(&tfull_bar[acc], acc_ph, bail)) break;
       ptx::tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
-      epilogue_tile<EPI, COMM, NBUF>(a, pm, taddr, mb, nb, q, lane, stage, stage_it);
+      if (COMM == kCommReduceScatterCe) {
+        // my own rows go straight into slot [me] of my staging buffer, the others into the send buffer
+        const int rpr = a.comm.rows_per_rank, me = a.comm.rank;
+        const int owner = min((mb * BM) / rpr, a.comm.nranks - 1);
+        __nv_bfloat16* cb = a.C;
+        if (owner == me)
+          cb = reinterpret_cast<__nv_bfloat16*>(const_cast<char*>(a.comm.stage_local) +
+                                                static_cast<size_t>(me) * rpr * a.N * 2) - static_cast<size_t>(me) * rpr * a.ldc;
+        epilogue_tile<EPI, kCommNone, NBUF>(a, pm, taddr, mb, nb, q, lane, stage, stage_it, cb);
+      } else {
+        epilogue_tile<EPI, COMM, NBUF>(a, pm, taddr, mb, nb, q, lane, stage, stage_it, a.C);
+      }
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive_cluster(tempty0 + acc * 8);
+      if (COMM == kCommReduceScatterCe && lane == 0) {
+        // this warp's rows of the tile are written: count them for the chunk (or own row block)
+        const int rpr = a.comm.rows_per_rank, me = a.comm.rank, n = a.comm.nranks, bpr = a.m_bpr;
+        const int owner = min((mb * BM) / rpr, n - 1);
+        __threadfence();
+        if (owner == me) {
+          ptx::red_release_sys_add_u32(a.comm.done_peer[me] + static_cast<size_t>(mb) * FLAG_STRIDE, 1u);
+        } else {
+          const int qq = (owner - me - 1 + n) % n;  // position of the slab in my schedule
+          const int j = mb - owner * bpr;
+          const int idx = qq * a.comm.ce_chunks + j / (bpr / a.comm.ce_chunks);
+          const uint32_t old = atomicAdd(a.comm.slab_count + idx, 1u);
+          if (old + 1 == a.comm.slab_target) {
+            __threadfence_system();
+            asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(a.comm.slab_flag + idx), "l"(1ull) : "memory");
+          }
+        }
+      }
       if (COMM == kCommReduceScatter) {
         if (tcount > 0) publish_tile<BN / 64>(a, prev_mb, lane, &warps_done[(tcount - 1) & 3]);
         prev_mb = mb;
@@ -1030,9 +1105,9 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   }
   if (threadIdx.x == 0 && *bail && a.err) atomicCAS(a.err, 0u, 0x47454d32u);
   if (a.times && cta_id == 0 && threadIdx.x == 0) a.times[1] = ptx::globaltimer_ns();
-  if (COMM == kCommReduceScatter && !*bail && !(a.debug & 1)) {
-    if (a.debug & 128) reduce_scatter_tail_direct(a, cta_id, a.gemm_ctas);
-    else reduce_scatter_tail(a, smem, bars + 24, bail, cta_id, a.gemm_ctas);
+  if ((COMM == kCommReduceScatter || COMM == kCommReduceScatterCe) && !*bail && !(a.debug & 1)) {
+    if (COMM == kCommReduceScatter && (a.debug & 128)) reduce_scatter_tail_direct(a, cta_id, a.gemm_ctas);
+    else reduce_scatter_tail(a, smem, bars + 24, bail, cta_id, a.gemm_ctas, COMM == kCommReduceScatterCe);
   }
 }
 

@@ -22,7 +22,7 @@ struct GemmLaunch {
 
 // Fusion descriptor filled by the tensor-parallel entry points.
 struct GemmFusion {
-  int role = 0;  // 0 none, 1 all-gather (push), 2 reduce-scatter (push + local sum)
+  int role = 0;  // 0 none, 1 all-gather, 2 reduce-scatter (TMA push + local sum), 3 reduce-scatter (copy engines + local sum)
   int rank = 0, nranks = 1;
   int comm_ctas = 0;         // all-gather: CTAs that move data (reduce-scatter reserves none)
   uint64_t timeout_ns = 0;
@@ -43,6 +43,12 @@ struct GemmFusion {
   uint32_t* done_peer[UCCL_MAX_LOCAL_RANKS] = {};
   void* rs_out = nullptr;
   int rs_ldo = 0;
+  // role 3 (reduce-scatter by copy engines): GemmLaunch.C is the local send buffer [M, N]; the
+  // chunks of a slab are counted and flagged here, arrivals from the other ranks are flagged in ce_done
+  uint32_t* slab_count = nullptr;
+  unsigned long long* slab_flag = nullptr;
+  const uint32_t* ce_done = nullptr;
+  int ce_chunks = 0;
 };
 
 ucclResult_t launchGemmBf16(const GemmLaunch& g, const GemmFusion* fusion, cudaStream_t stream);

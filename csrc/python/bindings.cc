@@ -221,6 +221,9 @@ PYBIND11_MODULE(_uccl_bindings, m) {
   });
 
   m.def("set_blocks", [](uintptr_t c, int blocks) { check(ucclCommSetBlocks(C(c), blocks), "ucclCommSetBlocks"); });
+  m.def("set_fused_rs_options", [](uintptr_t c, int rsMode, int ceChunks) {
+    check(ucclCommSetFusedRsOptions(C(c), rsMode, ceChunks), "ucclCommSetFusedRsOptions");
+  });
   m.def("set_fused_options", [](uintptr_t c, int agMode, int commCtas, int ceChunks) {
     check(ucclCommSetFusedOptions(C(c), agMode, commCtas, ceChunks), "ucclCommSetFusedOptions");
   });

@@ -283,6 +283,11 @@ ucclResult_t ucclCommSetBlocks(ucclComm_t comm, int blocks);
  * ceChunks: copies per peer (mode 1).
  * The environment variables UCCL_FUSED_AG / UCCL_FUSED_COMM_CTAS / UCCL_FUSED_CE_CHUNKS win. */
 ucclResult_t ucclCommSetFusedOptions(ucclComm_t comm, int agMode, int commCtas, int ceChunks);
+/* Options of the fused GEMM -> reduce-scatter; 0 keeps a default.  rsMode: 1 = the epilogue TMA-stores
+ * every tile into the owner's memory, 2 = tiles stay local and copy engines carry each finished
+ * chunk of a rank's rows to its owner (ceChunks chunks per rank, at most 8).  UCCL_FUSED_RS=kernel|ce
+ * and UCCL_FUSED_RS_CHUNKS win. */
+ucclResult_t ucclCommSetFusedRsOptions(ucclComm_t comm, int rsMode, int ceChunks);
 
 #ifdef __cplusplus
 }

@@ -301,9 +301,11 @@ def case_tp_mlp(comm, rank, n, args):
     dev = _dev(comm, rank)
     fail = []
     # every way of moving the all-gather's rows: copy engines, dedicated CTAs, a forwarder warp per CTA
-    for ag_mode in (("ce", "kernel", "spread") if n > 1 else ("ce",)):
+    modes = [("ce", "kernel"), ("kernel", "kernel"), ("spread", "ce"), ("ce", "ce")] if n > 1 else [("ce", "kernel")]
+    for ag_mode, rs_mode in modes:
         os.environ["UCCL_FUSED_AG"] = ag_mode
-        for hidden, ffn, tokens in ((512, 1024, 256 * n), (1024, 3584 * 2, 128 * n)):
+        os.environ["UCCL_FUSED_RS"] = rs_mode
+        for hidden, ffn, tokens in ((512, 1024, 256 * n), (1024, 3584 * 2, 128 * n), (512, 2048, 1024 * n)):
             mlp = TensorParallelMLP(comm, hidden, ffn, tokens, seed=3)
             x_full = torch.randn(tokens, hidden, generator=torch.Generator().manual_seed(11)).to(torch.bfloat16).to(dev)
             rows = tokens // n
@@ -319,10 +321,11 @@ def case_tp_mlp(comm, rank, n, args):
             err = (y.float() - ref).abs().max().item()
             scale = ref.abs().max().item()
             if not err <= 3e-2 * scale + 1e-3:
-                fail.append((ag_mode, hidden, ffn, tokens, err, scale))
+                fail.append((ag_mode, rs_mode, hidden, ffn, tokens, err, scale))
             if not torch.equal(gathered, x_full):
                 fail.append((ag_mode, "x_full not gathered", hidden, tokens))
     os.environ.pop("UCCL_FUSED_AG", None)
+    os.environ.pop("UCCL_FUSED_RS", None)
     return {"fail": fail, "nvls": comm.info["nvls"], "async": comm.async_error(), "last": comm.last_error()}
 
 

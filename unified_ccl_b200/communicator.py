@@ -276,6 +276,12 @@ class Communicator:
         GEMM launch) or ``"spread"`` (a forwarder warp in every GEMM CTA); 0 keeps a default."""
         _C.set_fused_options(self._comm, {"auto": 0, "ce": 1, "kernel": 2, "spread": 3}[ag_mode], int(comm_ctas), int(ce_chunks))
 
+    def set_fused_rs_options(self, rs_mode: str = "auto", ce_chunks: int = 0):
+        """How the GEMM -> reduce-scatter fusion moves its tiles: ``"kernel"`` (the epilogue TMA-stores every
+        tile into the owner's memory) or ``"ce"`` (tiles stay local, copy engines carry each finished chunk
+        of a rank's rows to its owner, ``ce_chunks`` chunks per rank)."""
+        _C.set_fused_rs_options(self._comm, {"auto": 0, "kernel": 1, "ce": 2}[rs_mode], int(ce_chunks))
+
     def load_tuning(self, path: str):
         _C.load_tuning(self._comm, path)
 

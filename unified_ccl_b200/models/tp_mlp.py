@@ -80,6 +80,35 @@ class TensorParallelMLP:
         self.ag_choice = cands[best]
         return {cands[i]: round(avg[i], 1) for i in range(len(cands))}
 
+    # candidates of autotune_rs(): (reduce-scatter mode, copy-engine chunks per rank)
+    RS_CANDIDATES = (("kernel", 0), ("ce", 1), ("ce", 2), ("ce", 4), ("ce", 8))
+
+    def autotune_rs(self, iters: int = 3, candidates=None):
+        """The same for the GEMM -> reduce-scatter half (``self.h`` must hold activations, e.g. after one
+        forward pass)."""
+        if self.tp == 1:
+            return {}
+        cands = tuple(candidates or self.RS_CANDIDATES)
+        times = torch.zeros(len(cands), device=self.h.device, dtype=torch.float32)
+        stream = torch.cuda.current_stream(self.h.device)
+        for i, (mode, chunks) in enumerate(cands):
+            self.comm.set_fused_rs_options(mode, chunks)
+            gemm_reduce_scatter(self.comm, self.h, self.w_down, self.c_partial, out=self.y)  # warm-up
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record(stream)
+            for _ in range(iters):
+                gemm_reduce_scatter(self.comm, self.h, self.w_down, self.c_partial, out=self.y)
+            e.record(stream)
+            e.synchronize()
+            times[i] = s.elapsed_time(e) * 1e3 / iters
+        self.comm.allreduce(times)
+        stream.synchronize()
+        avg = (times / self.tp).tolist()
+        best = min(range(len(cands)), key=lambda i: avg[i])
+        self.comm.set_fused_rs_options(*cands[best])
+        self.rs_choice = cands[best]
+        return {cands[i]: round(avg[i], 1) for i in range(len(cands))}
+
     def reference(self, x_full: torch.Tensor) -> torch.Tensor:
         """fp32 PyTorch restatement of this rank's partial result (before the reduce-scatter)."""
         fs = self.ffn // self.tp
