@@ -301,11 +301,17 @@ def case_tp_mlp(comm, rank, n, args):
     dev = _dev(comm, rank)
     fail = []
     # every way of moving the all-gather's rows: copy engines, dedicated CTAs, a forwarder warp per CTA
-    modes = [("ce", "kernel"), ("kernel", "kernel"), ("spread", "ce"), ("ce", "ce")] if n > 1 else [("ce", "kernel")]
+    modes = [("ce", "kernel"), ("kernel", "kernel"), ("spread", "kernel")] if n > 1 else [("ce", "kernel")]
+    # the copy-engine reduce-scatter is opt-in until it has been run on GPUs
+    if n > 1 and os.environ.get("UCCL_TEST_FUSED_RS_CE"):
+        modes += [("spread", "ce"), ("ce", "ce")]
     for ag_mode, rs_mode in modes:
         os.environ["UCCL_FUSED_AG"] = ag_mode
         os.environ["UCCL_FUSED_RS"] = rs_mode
-        for hidden, ffn, tokens in ((512, 1024, 256 * n), (1024, 3584 * 2, 128 * n), (512, 2048, 1024 * n)):
+        shapes = [(512, 1024, 256 * n), (1024, 3584 * 2, 128 * n)]
+        if rs_mode == "ce":
+            shapes.append((512, 2048, 1024 * n))  # several chunks per rank
+        for hidden, ffn, tokens in shapes:
             mlp = TensorParallelMLP(comm, hidden, ffn, tokens, seed=3)
             x_full = torch.randn(tokens, hidden, generator=torch.Generator().manual_seed(11)).to(torch.bfloat16).to(dev)
             rows = tokens // n
