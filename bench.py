@@ -26,7 +26,7 @@ BATCH, SEQ, HIDDEN, FFN = 4, 4096, 4096, 14336
 
 def reference_arm():
     # The reference is SYCL / Level-Zero code for Intel GPUs with a CMake + icpx build and no
-    # setup.py / pyproject.toml; `pip install --target baseline/_ref /root/reference` answers
+    # setup.py / pyproject.toml: `pip install --target baseline/_ref <reference tree>` answers
     # "Neither 'setup.py' nor 'pyproject.toml' found", and there is no icpx on this image.
     print(json.dumps({"impl": "reference",
                       "unavailable": "reference is Intel SYCL/Level-Zero code built with icpx+CMake: not pip-installable "

@@ -2,7 +2,7 @@
 """Bus-bandwidth sweep of every collective and algorithm against NCCL on the same GPUs.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \\
-        --master-port 29500 benchmarks/sweep.py --out gpurun_out/sweep_N.jsonl --tune gpurun_out/tune_N.json
+        --master-port 29500 benchmarks/sweep.py --out sweep_N.jsonl --tune tune_N.json
 
 Every number is device-timed (CUDA events on the launching stream around `iters` back-to-back
 calls, after warm-up, barrier + synchronize on both sides) and is the MAX over ranks.  Bus

@@ -255,6 +255,17 @@ def case_api_contract(comm, rank, n, args):
             fail.append(("bad fused option accepted", bad))
         except Exception:
             pass
+    comm.set_fused_options("spread")
+    comm.set_fused_options()
+    comm.set_fused_rs_options("ce", 4)
+    comm.set_fused_rs_options("kernel")
+    comm.set_fused_rs_options()
+    for bad in (("ce", 9), ("ce", -1)):
+        try:
+            comm.set_fused_rs_options(*bad)
+            fail.append(("bad fused reduce-scatter option accepted", bad))
+        except Exception:
+            pass
     comm.destroy()
     comm.destroy()  # idempotent
     return {"fail": fail}
