@@ -13,20 +13,21 @@
 // gemm2_bf16_kernel (a cluster of two CTAs per 256 x 256 tile, tcgen05 cta_group::2).
 //
 // Fusions (the reference has no GEMM at all; these exist for the tensor-parallel MLP block):
-//   all-gather -> GEMM : the first `comm_ctas` CTAs of the launch push this rank's activation rows
-//       to every rank with bulk TMA copies (local shard -> shared memory -> the same rows of every
-//       rank's A buffer; remote writes are posted, so one elected thread per CTA keeps the link
-//       busy), and add to a per-row-block arrival counter on the receiving rank once the copies of
-//       a piece have completed; the GEMM producer waits on the counter of the row block it is about
-//       to load, and reads this rank's own rows from the shard itself.  Tiles are visited in
-//       arrival order (own shard first, then block j of every peer for j = 0, 1, ...).
+//   all-gather -> GEMM : the GEMM producer waits on an arrival counter per 128-row block of A and
+//       reads this rank's own rows from the shard itself; tiles are visited in arrival order.  The
+//       rows are moved either by copy engines on side streams (host side, see
+//       allGatherPushBegin), or by the first `comm_ctas` CTAs of the launch, or by a forwarder
+//       warp in every GEMM CTA ("spread"); the last two run comm_allgather_push: bulk TMA copies
+//       local shard -> shared memory -> the same rows of every rank's A buffer, and an add to the
+//       receiving rank's counter once the copies of a piece have completed.
 //   GEMM -> reduce-scatter : the epilogue converts each accumulator tile to bf16, stages it in
 //       shared memory and TMA-stores it straight into slot [my rank] of the staging buffer of the
 //       rank that owns those rows; the accumulator is handed back to the MMA warp as soon as it
 //       has been read, and the owner's counter for the row block is bumped one tile later, when
 //       the stores have completed.  When its tiles are done every CTA helps to sum the n staged
 //       copies of this rank's own rows in fp32 (local loads only) into the output.  No SM is
-//       reserved for communication.
+//       reserved for communication.  In the copy-engine variant the epilogue only writes local
+//       memory and counts finished chunks; side streams carry them (reduceScatterPushBegin).
 // Every TMA load writes only the shared memory of the CTA that issued it; peers' memory is
 // reached with plain (non-replicating) bulk copies.
 //
@@ -177,7 +178,7 @@ __device__ __forceinline__ bool wait_flag_geq(const uint32_t* flag, uint32_t tar
 __device__ __forceinline__ int order_rows(const Args& a, int m, int tiles_rows, int unit) {
   if (a.m_order == 1) {
     // all-gather: my own shard first (it is already here), then row block j of every other
-    // shard for j = 0, 1, ... -- the order in which the pulls complete
+    // shard for j = 0, 1, ... -- the order in which the pushed blocks arrive
     const int bpr = a.m_bpr / unit, n = a.comm.nranks, r = a.comm.rank;
     if (m < bpr) return r * bpr + m;
     const int i = m - bpr, j = i / (n - 1), q = i % (n - 1) + 1;
