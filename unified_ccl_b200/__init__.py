@@ -20,4 +20,15 @@ __version__ = "0.1.0"
 
 from .communicator import Communicator, Window, get_unique_id  # noqa: E402,F401
 
-__all__ = ["Communicator", "Window", "get_unique_id"]
+
+
+def tuning_table(name: str = "b200_x8_nvswitch") -> str:
+    """Path of a measured tuner table shipped with the package (written by ``benchmarks/sweep.py --tune``
+    on the named machine); pass it to ``Communicator.load_tuning`` or set ``UCCL_TUNE_FILE``."""
+    path = _os.path.join(_os.path.dirname(_os.path.abspath(__file__)), "tuning", name + ".json")
+    if not _os.path.exists(path):
+        raise FileNotFoundError(path)
+    return path
+
+
+__all__ = ["Communicator", "Window", "get_unique_id", "tuning_table"]
