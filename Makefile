@@ -50,7 +50,26 @@ $(PYMOD): csrc/python/bindings.cc $(LIB) $(wildcard include/*.h)
 $(PLUGIN): plugins/sample/plugin.cc include/uccl_net.h include/uccl.h
 	$(CXX) $(CXXFLAGS) -shared $< -o $@
 
+# Host runtime under sanitizers: the native self tests (bootstrap, FIFO / proxy state machine,
+# plugin loader, ring schedules, tuner, groups, CPU collectives) as a plain executable.
+SAN_FLAGS_asan := -fsanitize=address,undefined -fno-omit-frame-pointer
+SAN_FLAGS_tsan := -fsanitize=thread
+
+define SAN_RULES
+$(BUILD)/$(1)/%.o: %.cc $$(wildcard include/*.h csrc/*/*.h)
+	@mkdir -p $$(dir $$@)
+	$$(CXX) $$(filter-out -O2,$$(CXXFLAGS)) -O1 $$(SAN_FLAGS_$(1)) -c $$< -o $$@
+
+$(BUILD)/$(1)/selftest: $$(patsubst %.cc,$(BUILD)/$(1)/%.o,$$(CC_SRCS)) $(BUILD)/$(1)/tests/native/selftest_main.o $$(CU_OBJS)
+	$$(CXX) $$(SAN_FLAGS_$(1)) -o $$@ $$^ -L$$(CUDA_HOME)/lib64 -lcudart_static -ldl -lpthread -lrt
+
+$(1): $(BUILD)/$(1)/selftest
+	$(BUILD)/$(1)/selftest
+endef
+$(eval $(call SAN_RULES,asan))
+$(eval $(call SAN_RULES,tsan))
+
 clean:
 	rm -rf $(BUILD) $(LIB) $(PYMOD) $(PLUGIN)
 
-.PHONY: all clean
+.PHONY: all clean asan tsan

@@ -391,7 +391,7 @@ ucclResult_t enqueueCopyEngine(Comm* c, const CollOp& op) {
     UCCL_TRY(copy(stage, send + po, len, s));
     UCCL_TRY(barrierOnStream(c, s));
     UCCL_TRY(forkStreams(c, s));
-    const size_t slotStride = (shardLen(n - 1) > shard ? shardLen(n - 1) : shard) + 15 & ~size_t(15);
+    const size_t slotStride = ((shardLen(n - 1) > shard ? shardLen(n - 1) : shard) + 15) & ~size_t(15);
     for (int k = 0; k < n; ++k) {
       const int p = (me + k) % n;
       UCCL_TRY(copy(stage + third + static_cast<size_t>(p) * slotStride, stagePeer[p] + shardOff(me), shardLen(me), c->ceStream[p]));
