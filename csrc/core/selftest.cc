@@ -13,6 +13,7 @@
 #include <functional>
 #include <set>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "../host/host_coll.h"
@@ -639,6 +640,54 @@ std::string testApiRules() {
   return "";
 }
 
+// ------------------------------------------------------------------ CPU ranks as threads of one process
+// ucclCommInitAll on the host backend: three communicators, one thread each, through the real
+// bootstrap, proxy threads, FIFOs and the socket plugin.  Under ThreadSanitizer this is the race
+// check of the whole host data path.
+std::string testCpuRankThreads() {
+  const char* prevBackend = getenv("UCCL_BACKEND");
+  const std::string keep = prevBackend ? prevBackend : "";
+  const char* prevIf = getenv("UCCL_BOOTSTRAP_IFNAME");
+  const std::string keepIf = prevIf ? prevIf : "";
+  setenv("UCCL_BACKEND", "cpu", 1);
+  setenv("UCCL_BOOTSTRAP_IFNAME", "lo", 1);
+  constexpr int n = 3;
+  constexpr size_t count = 70001;  // not a multiple of anything
+  ucclComm_t comms[n] = {};
+  ucclResult_t rc = ucclCommInitAll(comms, n, nullptr);
+  std::string fail;
+  if (rc == ucclSuccess) {
+    std::vector<std::vector<float>> buf(n, std::vector<float>(count));
+    std::vector<std::vector<float>> gathered(n, std::vector<float>(count * n));
+    for (int r = 0; r < n; ++r)
+      for (size_t i = 0; i < count; ++i) buf[r][i] = static_cast<float>(r + 1) + static_cast<float>(i % 7);
+    std::vector<ucclResult_t> res(n, ucclSuccess);
+    std::vector<std::thread> th;
+    for (int r = 0; r < n; ++r)
+      th.emplace_back([&, r] {
+        ucclResult_t e = ucclAllGather(buf[r].data(), gathered[r].data(), count, ucclFloat32, comms[r], nullptr);
+        if (e == ucclSuccess) e = ucclAllReduce(buf[r].data(), buf[r].data(), count, ucclFloat32, ucclSum, comms[r], nullptr);
+        res[r] = e;
+      });
+    for (auto& t : th) t.join();
+    for (int r = 0; r < n && fail.empty(); ++r) {
+      if (res[r] != ucclSuccess) fail = std::string("collective failed: ") + ucclGetErrorString(res[r]);
+      for (size_t i = 0; i < count && fail.empty(); i += 997) {
+        const float want = 6.f + 3.f * static_cast<float>(i % 7);
+        if (buf[r][i] != want) fail = "wrong all-reduce value";
+        for (int s = 0; s < n; ++s)
+          if (gathered[r][s * count + i] != static_cast<float>(s + 1) + static_cast<float>(i % 7)) fail = "wrong all-gather value";
+      }
+    }
+    for (int r = 0; r < n; ++r) ucclCommDestroy(comms[r]);
+  } else {
+    fail = std::string("ucclCommInitAll: ") + ucclGetErrorString(rc);
+  }
+  if (prevBackend) setenv("UCCL_BACKEND", keep.c_str(), 1); else unsetenv("UCCL_BACKEND");
+  if (prevIf) setenv("UCCL_BOOTSTRAP_IFNAME", keepIf.c_str(), 1); else unsetenv("UCCL_BOOTSTRAP_IFNAME");
+  return fail;
+}
+
 struct Case {
   const char* name;
   std::function<std::string()> fn;
@@ -658,6 +707,7 @@ const std::vector<Case>& cases() {
       {"conversions", testConversions},
       {"config", testConfig},
       {"api_rules", testApiRules},
+      {"cpu_rank_threads", testCpuRankThreads},
   };
   return all;
 }
