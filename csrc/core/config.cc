@@ -3,7 +3,9 @@
 #include <ctype.h>
 #include <stdlib.h>
 #include <string.h>
+#include <stdint.h>
 #include <strings.h>
+#include <time.h>
 
 #include "log.h"
 
@@ -109,9 +111,23 @@ Config loadConfig() {
   if ((s = getenv("UCCL_TRACE_FILE")) && *s) c.traceFile = s;
   c.netChunkBytes = parseSize(getenv("UCCL_NET_CHUNK_BYTES"), 512u << 10);
   if (c.netChunkBytes < 4096) c.netChunkBytes = 4096;
+  c.jitterUs = (int)envLong("UCCL_JITTER_US", 0);
+  if (c.jitterUs < 0) c.jitterUs = 0;
   c.fusedCeChunks = (int)envLong("UCCL_FUSED_CE_CHUNKS", 0);
   if (c.fusedCeChunks < 0) c.fusedCeChunks = 0;
   return c;
+}
+
+void jitterPause(int maxUs) {
+  if (maxUs <= 0) return;
+  static thread_local uint64_t state = 0x9e3779b97f4a7c15ull ^ reinterpret_cast<uintptr_t>(&state);
+  state ^= state << 13;
+  state ^= state >> 7;
+  state ^= state << 17;
+  const long us = static_cast<long>(state % static_cast<uint64_t>(maxUs + 1));
+  if (us == 0) return;
+  struct timespec ts = {0, us * 1000};
+  nanosleep(&ts, nullptr);
 }
 
 }  // namespace uccl

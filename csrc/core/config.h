@@ -35,10 +35,16 @@ struct Config {
   int p2pMode = 0;                       // UCCL_P2P = 0 auto, 1 cudaIpc, 2 vmm
   std::string traceFile;                 // UCCL_TRACE_FILE
   size_t netChunkBytes = 512u << 10;     // UCCL_NET_CHUNK_BYTES (bounce slot size)
+  int jitterUs = 0;                      // UCCL_JITTER_US: random host-side pauses of up to this many microseconds (testing)
   int fusedCeChunks = 0;                 // UCCL_FUSED_CE_CHUNKS: copies per peer of the copy-engine all-gather
 };
 
 Config loadConfig();
+
+// Schedule perturbation for tests: sleeps a pseudo-random time in [0, maxUs] microseconds (per-thread
+// generator); a no-op when maxUs <= 0.  Called between the steps of the proxy thread and of the
+// host-driven transfer loop so that orderings which normally never occur get exercised.
+void jitterPause(int maxUs);
 
 // Parsers exposed for unit tests.
 bool parseAlgo(const char* s, ucclAlgo_t* out);

@@ -125,6 +125,7 @@ ucclResult_t hostRunXfers(Comm* comm, std::vector<HostXfer>& xfers) {
   uint32_t idle = 0;
   while (remaining) {
     bool moved = false;
+    jitterPause(comm->cfg.jitterUs);
     for (HostXfer& x : xfers) {
       if (x.len == 0) continue;
       const size_t slot = x.conns[0]->slotBytes;

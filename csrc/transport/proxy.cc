@@ -89,6 +89,7 @@ static void proxyMain(Comm* comm) {
     }
     uint64_t posts = 0, completions = 0;
     for (NetConn* c : conns) {
+      jitterPause(comm->cfg.jitterUs);
       ucclResult_t r = proxyProgressConn(comm->net, c, &posts, &completions);
       if (r != ucclSuccess) {
         commSetError(comm, "network %s to/from rank %d failed: %s", c->isSend ? "send" : "receive", c->peer,

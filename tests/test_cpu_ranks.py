@@ -66,3 +66,12 @@ def test_rank_that_exits_between_steps():
         assert "died" not in r and not r["fail"], r
         assert r["seconds"] < 30
     assert res[-1]["left"]
+
+
+@pytest.mark.parametrize("jitter_us", [50, 400])
+def test_collective_matrix_with_schedule_perturbation(jitter_us):
+    """Random pauses between the steps of the proxy threads and of the host transfer loops: the
+    results must not depend on the interleaving (UCCL_JITTER_US)."""
+    env = dict(CPU, UCCL_JITTER_US=str(jitter_us))
+    assert_all_ok(run_ranks("collectives_small", 3, env=env, timeout=300))
+    assert_all_ok(run_ranks("sendrecv", 4, env=env, timeout=300))
