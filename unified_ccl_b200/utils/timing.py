@@ -40,34 +40,102 @@ def device_time_ms(fn, iters=20, warmup=5, flush=True, pre=None):
 
 
 class ClockSampler:
-    """Samples SM clock, power and throttle reasons with nvidia-smi while a region runs."""
+    """Samples SM clock, power and throttle reasons while a region runs.
+
+    Reads NVML in a thread of this process every ``period_ms`` (so that even a region of a few
+    milliseconds gets samples); falls back to an ``nvidia-smi -lms`` child when the NVML module
+    is not importable.  Only reads: no clock, power or mode setting is touched."""
 
     QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
+    # NVML clocks-event (throttle) reason bits
+    REASON_BITS = {"sw_power_cap": 0x4, "hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
 
-    def __init__(self, gpu_index=0, period_ms=50):
+    def __init__(self, gpu_index=0, period_ms=2):
         self.gpu_index, self.period_ms = gpu_index, period_ms
         self.samples, self._proc, self._thread = [], None, None
+        self._stop = threading.Event()
+        self._nvml = None
+        self._handle = None
 
-    def __enter__(self):
+    # ---- NVML path
+    def _nvml_open(self):
         try:
-            self._proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(self.gpu_index), f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", str(self.period_ms)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self._thread = threading.Thread(target=self._read, daemon=True)
-            self._thread.start()
-        except OSError:
-            self._proc = None
-        return self
+            import pynvml
+            pynvml.nvmlInit()
+            handle = None
+            try:
+                import torch
+                uuid = getattr(torch.cuda.get_device_properties(self.gpu_index), "uuid", None)
+                if uuid is not None:
+                    u = str(uuid)
+                    handle = pynvml.nvmlDeviceGetHandleByUUID(u if u.startswith("GPU-") else "GPU-" + u)
+            except Exception:  # noqa: BLE001 - any failure falls back to the plain index
+                handle = None
+            if handle is None:
+                handle = pynvml.nvmlDeviceGetHandleByIndex(self.gpu_index)
+            self._nvml, self._handle = pynvml, handle
+            return True
+        except Exception:  # noqa: BLE001
+            self._nvml = None
+            return False
 
+    def _nvml_sample(self):
+        n, h = self._nvml, self._handle
+        sm = n.nvmlDeviceGetClockInfo(h, n.NVML_CLOCK_SM)
+        mx = n.nvmlDeviceGetMaxClockInfo(h, n.NVML_CLOCK_SM)
+        try:
+            watts = n.nvmlDeviceGetPowerUsage(h) / 1000.0
+        except Exception:  # noqa: BLE001
+            watts = 0.0
+        getter = getattr(n, "nvmlDeviceGetCurrentClocksEventReasons", None) or getattr(
+            n, "nvmlDeviceGetCurrentClocksThrottleReasons")
+        bits = int(getter(h))
+        row = [str(sm), str(mx), "%.1f" % watts]
+        for name in ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"):
+            row.append("Active" if bits & self.REASON_BITS[name] else "Not Active")
+        self.samples.append(row)
+
+    def _nvml_loop(self):
+        while not self._stop.is_set():
+            try:
+                self._nvml_sample()
+            except Exception:  # noqa: BLE001
+                break
+            self._stop.wait(self.period_ms / 1000.0)
+
+    # ---- nvidia-smi path
     def _read(self):
         for line in self._proc.stdout:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) >= 7:
                 self.samples.append(parts)
 
+    def __enter__(self):
+        if self._nvml_open():
+            self._thread = threading.Thread(target=self._nvml_loop, daemon=True)
+            self._thread.start()
+            return self
+        try:
+            self._proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu_index), f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", str(max(self.period_ms, 20))], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self._thread = threading.Thread(target=self._read, daemon=True)
+            self._thread.start()
+        except OSError:
+            self._proc = None
+        return self
+
     def __exit__(self, *exc):
+        self._stop.set()
+        if self._nvml is not None:
+            if self._thread:
+                self._thread.join(timeout=1)
+            try:
+                self._nvml.nvmlShutdown()
+            except Exception:  # noqa: BLE001
+                pass
         if self._proc:
             self._proc.terminate()
             try:
@@ -79,7 +147,7 @@ class ClockSampler:
     def summary(self):
         sm, mx, reasons = [], 0, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for s in self.samples:
+        for s in list(self.samples):
             try:
                 sm.append(float(s[0]))
                 mx = max(mx, float(s[1]))
