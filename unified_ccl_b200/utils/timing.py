@@ -52,7 +52,7 @@ class ClockSampler:
     # NVML clocks-event (throttle) reason bits
     REASON_BITS = {"sw_power_cap": 0x4, "hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
 
-    def __init__(self, gpu_index=0, period_ms=2):
+    def __init__(self, gpu_index=0, period_ms=5):
         self.gpu_index, self.period_ms = gpu_index, period_ms
         self.samples, self._proc, self._thread = [], None, None
         self._stop = threading.Event()
