@@ -6,7 +6,7 @@
   * one-sided put+signal ping-pong latency vs NCCL send/recv ping-pong
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \\
-        --master-port 29500 benchmarks/fused_layers.py --what norm,moe,rma
+        --master-port 29500 benchmarks/fused_layers.py --what norm,moe,rma   (add norm_breakdown for the phases of the norm kernel)
 
 Times are CUDA-event times on the launching stream, max over ranks, after warm-up.
 """
@@ -93,6 +93,22 @@ def main():
         emit({"bench": "allreduce_residual_rmsnorm", "n": n, "tokens": T, "hidden": H, "fused_us": round(us_f, 1),
               "nccl_plus_norm_us": round(us_b, 1), "speedup": round(us_b / us_f, 3), "roofline_ring_us": round(roof, 1),
               "roofline_switch_us": round(roof_nvls, 1), "frac_of_ring_roofline": round(roof / us_f, 3), "nvls": comm.info["nvls"]})
+        if "norm_breakdown" in what and n > 1:
+            # the same kernel with a phase left out (UCCL_NORM_DEBUG), and the two data paths
+            parts = {}
+            for bits, name in ((1, "no_phase_b"), (2, "no_phase_a_stores"), (3, "loads_only"), (4, "phase_b_only")):
+                os.environ["UCCL_NORM_DEBUG"] = str(bits)
+                parts[name] = round(timed(lambda: allreduce_residual_rmsnorm(comm, x, res, gamma, 1e-6, out=out, residual_out=res)), 1)
+            os.environ["UCCL_NORM_DEBUG"] = "0"
+            for algo in ("nvls", "two_shot"):
+                if algo == "nvls" and not comm.info["nvls"]:
+                    continue
+                comm.set_algo(algo)
+                parts["path_" + algo] = round(timed(lambda: allreduce_residual_rmsnorm(comm, x, res, gamma, 1e-6, out=out, residual_out=res)), 1)
+            comm.set_algo("auto")
+            parts["allreduce_same_bytes"] = round(timed(lambda: comm.allreduce(x)), 1)
+            parts["nccl_allreduce_same_bytes"] = round(timed(lambda: dist.all_reduce(xn)), 1)
+            emit({"bench": "allreduce_residual_rmsnorm_breakdown", "n": n, "tokens": T, "hidden": H, "us": parts})
         comm.free(x)
         comm.free(res)
 
