@@ -63,15 +63,20 @@ class TensorParallelMLP:
         times = torch.zeros(len(cands), device=self.h.device, dtype=torch.float32)
         stream = torch.cuda.current_stream(self.h.device)
         for i, (mode, ctas, chunks) in enumerate(cands):
-            self.comm.set_fused_options(mode, ctas, chunks)
-            allgather_gemm(self.comm, x_shard, self.x_full, self.w_gate_up, out=self.h, swiglu=True)  # warm-up
-            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            s.record(stream)
-            for _ in range(iters):
-                allgather_gemm(self.comm, x_shard, self.x_full, self.w_gate_up, out=self.h, swiglu=True)
-            e.record(stream)
-            e.synchronize()
-            times[i] = s.elapsed_time(e) * 1e3 / iters
+            try:
+                self.comm.set_fused_options(mode, ctas, chunks)
+                allgather_gemm(self.comm, x_shard, self.x_full, self.w_gate_up, out=self.h, swiglu=True)  # warm-up
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s.record(stream)
+                for _ in range(iters):
+                    allgather_gemm(self.comm, x_shard, self.x_full, self.w_gate_up, out=self.h, swiglu=True)
+                e.record(stream)
+                e.synchronize()
+                times[i] = s.elapsed_time(e) * 1e3 / iters
+            except (ValueError, RuntimeError):
+                # a setting this shape does not allow (refused before anything is launched, on
+                # every rank alike): out of the running
+                times[i] = 1e9
         self.comm.allreduce(times)
         stream.synchronize()
         avg = (times / self.tp).tolist()
@@ -92,15 +97,18 @@ class TensorParallelMLP:
         times = torch.zeros(len(cands), device=self.h.device, dtype=torch.float32)
         stream = torch.cuda.current_stream(self.h.device)
         for i, (mode, chunks) in enumerate(cands):
-            self.comm.set_fused_rs_options(mode, chunks)
-            gemm_reduce_scatter(self.comm, self.h, self.w_down, self.c_partial, out=self.y)  # warm-up
-            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            s.record(stream)
-            for _ in range(iters):
-                gemm_reduce_scatter(self.comm, self.h, self.w_down, self.c_partial, out=self.y)
-            e.record(stream)
-            e.synchronize()
-            times[i] = s.elapsed_time(e) * 1e3 / iters
+            try:
+                self.comm.set_fused_rs_options(mode, chunks)
+                gemm_reduce_scatter(self.comm, self.h, self.w_down, self.c_partial, out=self.y)  # warm-up
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s.record(stream)
+                for _ in range(iters):
+                    gemm_reduce_scatter(self.comm, self.h, self.w_down, self.c_partial, out=self.y)
+                e.record(stream)
+                e.synchronize()
+                times[i] = s.elapsed_time(e) * 1e3 / iters
+            except (ValueError, RuntimeError):
+                times[i] = 1e9
         self.comm.allreduce(times)
         stream.synchronize()
         avg = (times / self.tp).tolist()
