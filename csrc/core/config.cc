@@ -94,7 +94,16 @@ Config loadConfig() {
   if ((s = getenv("UCCL_NET_PLUGIN")) && *s) c.netPlugin = s;
   c.forceNet = envLong("UCCL_FORCE_NET", 0) == 1;
   if ((s = getenv("UCCL_TUNE_FILE")) && *s) c.tuneFile = s;
-  c.waitTimeoutMs = (uint64_t)envLong("UCCL_WAIT_TIMEOUT_MS", 10000);
+  {
+    // every device-side wait stays bounded: 1 ms .. 10 min, whatever the variable says
+    long ms = envLong("UCCL_WAIT_TIMEOUT_MS", 10000);
+    if (ms < 1 || ms > 600000) {
+      const long clamped = ms < 1 ? 1 : 600000;
+      UCCL_LOG(WARN, "UCCL_WAIT_TIMEOUT_MS=%ld is outside [1, 600000]; using %ld", ms, clamped);
+      ms = clamped;
+    }
+    c.waitTimeoutMs = (uint64_t)ms;
+  }
   c.nvls = (int)envLong("UCCL_NVLS", -1);
   if ((s = getenv("UCCL_BOOTSTRAP_IFNAME")) && *s) c.bootstrapIf = s;
   c.bootstrapPort = (int)envLong("UCCL_BOOTSTRAP_PORT", 0);

@@ -578,19 +578,46 @@ ucclResult_t executeP2pBatch(Comm* c, const std::vector<CollOp>& ops) {
     return enqueueNetGpuP2p(c, rest);  // network path: staged through pinned host memory
   }
 
+  // Operations with the same peer and direction share one FIFO: they form a chain that runs in
+  // the order of the calls (two sends to one peer in a group are legal).  A launch carries the
+  // next kP2pChainDepth operations of every chain, so both ends of a FIFO cut a long group at the
+  // same places and no launch waits for an operation that its peer put into a later one.
   cudaStream_t stream = rest[0].stream;
-  for (size_t base = 0; base < rest.size(); base += kMaxP2pOps) {
+  std::vector<std::vector<const CollOp*>> chains;
+  std::vector<std::pair<int, bool>> keys;
+  for (const CollOp& op : rest) {
+    const std::pair<int, bool> key(c->peers[op.root].localRank, op.isSend);
+    size_t k = 0;
+    while (k < keys.size() && keys[k] != key) ++k;
+    if (k == keys.size()) {
+      keys.push_back(key);
+      chains.emplace_back();
+    }
+    chains[k].push_back(&op);
+  }
+  if (chains.size() > static_cast<size_t>(kMaxP2pChains)) return ucclInternalError;
+  size_t longest = 0;
+  for (const auto& ch : chains) longest = std::max(longest, ch.size());
+  for (size_t base = 0; base < longest; base += kP2pChainDepth) {
     P2pArgs a;
     memset(&a, 0, sizeof(a));
     a.dc = c->dev;
-    a.nops = static_cast<int>(std::min<size_t>(kMaxP2pOps, rest.size() - base));
-    for (int i = 0; i < a.nops; ++i) {
-      const CollOp& op = rest[base + i];
-      a.ops[i].isSend = op.isSend ? 1 : 0;
-      a.ops[i].peer = c->peers[op.root].localRank;
-      a.ops[i].src = static_cast<const char*>(op.send);
-      a.ops[i].dst = static_cast<char*>(op.recv);
-      a.ops[i].bytes = op.count * dataTypeSize(op.dtype);
+    int nops = 0;
+    for (size_t k = 0; k < chains.size(); ++k) {
+      int prev = -1;
+      for (size_t i = base; i < std::min(chains[k].size(), base + kP2pChainDepth); ++i) {
+        const CollOp& op = *chains[k][i];
+        P2pOp& d = a.ops[nops];
+        d.isSend = op.isSend ? 1 : 0;
+        d.peer = keys[k].first;
+        d.next = -1;
+        d.src = static_cast<const char*>(op.send);
+        d.dst = static_cast<char*>(op.recv);
+        d.bytes = op.count * dataTypeSize(op.dtype);
+        if (prev < 0) a.heads[a.nchains++] = nops;
+        else a.ops[prev].next = nops;
+        prev = nops++;
+      }
     }
     cudaError_t e = launchP2pKernel(a, stream);
     if (e != cudaSuccess) {

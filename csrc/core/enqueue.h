@@ -49,8 +49,9 @@ ucclResult_t allGatherPushBegin(Comm* c, const void* shard, char* const* fullPee
                                 size_t shardBytes, int blocksPerRank, bool copyOwn, int lanes, cudaStream_t s);
 ucclResult_t allGatherPushEnd(Comm* c, bool copyOwn, int lanes, cudaStream_t s);
 // copy-engine transport of the GEMM -> reduce-scatter fusion (see enqueue_ring_ce.cc)
-ucclResult_t reduceScatterPushBegin(Comm* c, const char* sendBuf, char* const* stagePeer, char* const* ceDonePeer,
-                                    unsigned long long* slabFlag, size_t slabBytes, int chunks, cudaStream_t s);
+ucclResult_t reduceScatterPushPrepare(Comm* c, cudaStream_t s);
+ucclResult_t reduceScatterPushCopies(Comm* c, const char* sendBuf, char* const* stagePeer, char* const* ceDonePeer,
+                                     unsigned long long* slabFlag, size_t slabBytes, int chunks);
 ucclResult_t reduceScatterPushEnd(Comm* c, unsigned long long* slabFlag, int nflags, cudaStream_t s);
 ucclResult_t enqueueNetGpu(Comm* c, const CollOp& op);
 ucclResult_t enqueueNetGpuP2p(Comm* c, const std::vector<CollOp>& ops);

@@ -185,8 +185,14 @@ ucclResult_t allGatherPushEnd(Comm* c, bool copyOwn, int lanes, cudaStream_t s) 
 // me+1, me+2, ...) when chunk ch of that slab is complete.  One side stream per peer waits for each
 // flag (a stream memory operation), copies the chunk into slot [me] of the peer's staging buffer
 // and then a one onto the peer's arrival flag [me][ch].
-ucclResult_t reduceScatterPushBegin(Comm* c, const char* sendBuf, char* const* stagePeer, char* const* ceDonePeer,
-                                    unsigned long long* slabFlag, size_t slabBytes, int chunks, cudaStream_t s) {
+//
+// Order of the three calls: Prepare, the kernel launch, Copies, End.  A stream parked on a memory
+// operation is invisible to CUDA's own dependency tracking, and streams share a limited number
+// of hardware queues: a kernel submitted behind such a wait in the same queue would never start,
+// and the wait would never end.  So nothing is parked before the kernel that raises the flags has
+// been submitted; afterwards a parked stream can at worst delay unrelated work until its flag
+// comes, which the running kernel guarantees.
+ucclResult_t reduceScatterPushPrepare(Comm* c, cudaStream_t s) {
   ucclResult_t r = ensureCeStreams(c);
   if (r != ucclSuccess) return r;
   if ((r = ensureOnes(c)) != ucclSuccess) return r;
@@ -195,9 +201,15 @@ ucclResult_t reduceScatterPushBegin(Comm* c, const char* sendBuf, char* const* s
     commSetError(c, "stream memory operations are not available");
     return ucclInvalidUsage;
   }
+  // everything enqueued on `s` so far (the zeroing of the flags, the rank barrier) comes first
+  if (cudaEventRecord(c->ceStart, s) != cudaSuccess) return cudaFail(c, "cudaEventRecord");
+  return ucclSuccess;
+}
+ucclResult_t reduceScatterPushCopies(Comm* c, const char* sendBuf, char* const* stagePeer, char* const* ceDonePeer,
+                                     unsigned long long* slabFlag, size_t slabBytes, int chunks) {
+  const DriverApi& d = driverApi();
   const int n = c->localRanks, me = c->localRank;
   const size_t chunkBytes = slabBytes / chunks;
-  if (cudaEventRecord(c->ceStart, s) != cudaSuccess) return cudaFail(c, "cudaEventRecord");
   for (int q = 0; q + 1 < n; ++q) {
     const int o = (me + 1 + q) % n;
     cudaStream_t st = c->ceStream[o];
@@ -330,7 +342,7 @@ ucclResult_t enqueueCopyEngine(Comm* c, const CollOp& op) {
   const char* send = static_cast<const char*>(op.send);
   char* recv = static_cast<char*>(op.recv);
   auto copy = [&](void* dst, const void* src, size_t bytes, cudaStream_t st) -> ucclResult_t {
-    if (bytes == 0) return ucclSuccess;
+    if (bytes == 0 || dst == src) return ucclSuccess;  // in place: my own part is already where it belongs
     if (cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, st) != cudaSuccess) return cudaFail(c, "cudaMemcpyAsync");
     return ucclSuccess;
   };

@@ -334,7 +334,9 @@ extern "C" ucclResult_t ucclGemmReduceScatter(const void* A, const void* W, void
   if (cudaMemsetAsync(done, 0, kGemmFlagStrideBytes * (M / 128), s) != cudaSuccess) return ucclSystemError;
   const int rsChunks = fusedRsCeChunks(c, M / n / 128);
   if (rsChunks > 0) {
-    // ---- copy engines carry the slabs (see reduceScatterPushBegin)
+    // ---- copy engines carry the slabs (see reduceScatterPushCopies)
+    // the kernel must be loaded before any side stream is parked on a flag that only it can raise
+    if ((r = preloadGemmKernels()) != ucclSuccess) return r;
     const size_t slabBytes = static_cast<size_t>(M / n) * N * 2;
     const size_t need = static_cast<size_t>(M) * N * 2;
     if (c->rsSendBytes < need) {
@@ -348,7 +350,13 @@ extern "C" ucclResult_t ucclGemmReduceScatter(const void* A, const void* W, void
       }
       c->rsSendBytes = need;
     }
-    if (!c->rsCtl && cudaMalloc(&c->rsCtl, 4096) != cudaSuccess) return ucclSystemError;
+    if (!c->rsCtl) {
+      if (cudaMalloc(&c->rsCtl, 4096) != cudaSuccess) return ucclSystemError;
+      // run once, here, the very memset that reduceScatterPushEnd issues while side streams are
+      // parked: whatever it needs loaded is loaded now
+      if (cudaMemsetAsync(static_cast<char*>(c->rsCtl) + 1024, 0xff, sizeof(unsigned long long) * (n - 1) * rsChunks, s) != cudaSuccess)
+        return ucclSystemError;
+    }
     uint32_t* slabCount = static_cast<uint32_t*>(c->rsCtl);
     unsigned long long* slabFlag = reinterpret_cast<unsigned long long*>(static_cast<char*>(c->rsCtl) + 1024);
     char* ceDone = c->arena->local + kArenaGemmCeDoneOff;
@@ -379,10 +387,15 @@ extern "C" ucclResult_t ucclGemmReduceScatter(const void* A, const void* W, void
     f.rs_ldo = N;
     g.C = c->rsSendBuf;
     commCount(c, ucclCollReduceScatter, static_cast<size_t>(M) * N * 2, ucclAlgoCopyEngine);
-    if ((r = reduceScatterPushBegin(c, static_cast<const char*>(c->rsSendBuf), stagePeer, ceDonePeer, slabFlag, slabBytes,
-                                    rsChunks, s)) != ucclSuccess)
-      return r;
+    if ((r = reduceScatterPushPrepare(c, s)) != ucclSuccess) return r;
     if ((r = launchGemmBf16(g, &f, s)) != ucclSuccess) return r;
+    // only now, with the kernel that raises the flags submitted, are the side streams parked on them
+    r = reduceScatterPushCopies(c, static_cast<const char*>(c->rsSendBuf), stagePeer, ceDonePeer, slabFlag, slabBytes, rsChunks);
+    if (r != ucclSuccess) {
+      // release whatever was parked before the failure, then report it
+      (void)reduceScatterPushEnd(c, slabFlag, (n - 1) * rsChunks, s);
+      return r;
+    }
     return reduceScatterPushEnd(c, slabFlag, (n - 1) * rsChunks, s);
   }
   if ((r = enqueueBarrier(c, s)) != ucclSuccess) return r;

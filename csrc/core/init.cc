@@ -585,3 +585,13 @@ extern "C" ucclResult_t ucclCommSetBlocks(ucclComm_t comm, int blocks) {
   c->forcedBlocks = blocks;
   return ucclSuccess;
 }
+
+// A unique id derived from a rendezvous address that every rank already knows (for launchers that
+// hand out MASTER_ADDR / MASTER_PORT): all ranks compute the same id, one of them serves it.
+extern "C" ucclResult_t ucclUniqueIdFromAddress(const char* ip, int port, uint64_t seed, ucclUniqueId* id) {
+  return uccl::bootstrapIdFromAddress(ip, port, seed, id);
+}
+extern "C" ucclResult_t ucclServeUniqueId(const ucclUniqueId* id) {
+  if (!id) return ucclInvalidArgument;
+  return uccl::bootstrapServeId(*id, uccl::loadConfig());
+}

@@ -47,6 +47,7 @@ void fillArgs(ucclMoeContext* m, MoeArgs* a) {
   a->topk = m->topk;
   const int n = c->nRanks;
   a->expertsPerRank = m->experts / n;
+  a->numExperts = m->experts;
   a->rowsPerSource = m->rows;
   if (n == 1) {
     a->dc.rank = 0;

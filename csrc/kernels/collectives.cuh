@@ -48,6 +48,22 @@ enum CollKernel : int {
 
 cudaError_t launchCollKernel(CollKernel k, const CollArgs& a, int blocks, cudaStream_t stream);
 
+// Reduce-scatter with a scale and an output element type of its own, see fused_cast.cu.
+struct CastArgs {
+  DevComm dc;
+  const char* in[UCCL_MAX_LOCAL_RANKS];  // every rank's input: nranks chunks, chunkStride bytes apart, peer-visible
+  const char* inMc;                      // multicast alias of `in` (switch reduction) or nullptr
+  const char* inUser;                    // set when `in` is the staging area: my input is copied in first
+  size_t inStride;                       // bytes between consecutive rank chunks in inUser
+  size_t chunkStride;                    // bytes between consecutive rank chunks in `in`
+  size_t chunkElems;                     // elements per rank chunk in this launch
+  int inType, outType;                   // ucclDataType_t
+  float scale;
+  char* out;                             // local: this rank's chunk in outType, 16-byte aligned
+  float* outScales;                      // fp8 output: one scale per 128 elements
+};
+cudaError_t launchReduceCastKernel(const CastArgs& a, int blocks, cudaStream_t stream);
+
 // Ring all-reduce / all-gather / reduce-scatter over peer-memory step FIFOs (Simple protocol)
 // and the LL128 line protocol; see ring.cu.
 struct RingArgs {
@@ -67,17 +83,24 @@ struct RingArgs {
 cudaError_t launchRingKernel(const RingArgs& a, int blocks, cudaStream_t stream);
 
 // Point-to-point: each entry is one send or one receive through the receiver's arena slots.
+// Operations with the same peer and the same direction share one FIFO, so they form a chain that
+// one set of CTAs runs in order (`next`); different chains run side by side.
 struct P2pOp {
   int isSend;
   int peer;       // NVLink-domain index
+  int next;       // next operation of the same (peer, direction) chain in this launch, or -1
+  int pad;
   const char* src;
   char* dst;
   size_t bytes;
 };
-constexpr int kMaxP2pOps = 32;
+constexpr int kMaxP2pChains = 2 * UCCL_MAX_LOCAL_RANKS;  // (peer, direction) pairs
+constexpr int kP2pChainDepth = 2;                        // operations of one chain per launch
+constexpr int kMaxP2pOps = kMaxP2pChains * kP2pChainDepth;
 struct P2pArgs {
   DevComm dc;
-  int nops;
+  int nchains;
+  int heads[kMaxP2pChains];  // first operation of every chain
   P2pOp ops[kMaxP2pOps];
 };
 cudaError_t launchP2pKernel(const P2pArgs& a, cudaStream_t stream);

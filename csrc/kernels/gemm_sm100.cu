@@ -124,7 +124,36 @@ bool usePairKernel() {
   return (s && *s) ? atoi(s) != 0 : true;
 }
 
+template <int EPI, int COMM>
+cudaError_t loadVariants() {
+  static thread_local int last1 = -1, last2 = -1;
+  static thread_local cudaError_t e1 = cudaSuccess, e2 = cudaSuccess;
+  cudaError_t e = ensureSmem(gemm::gemm_bf16_kernel<EPI, COMM>, &last1, &e1);
+  if (e != cudaSuccess) return e;
+  return ensureSmem(gemm::gemm2_bf16_kernel<EPI, COMM>, &last2, &e2);
+}
+
 }  // namespace
+
+ucclResult_t preloadGemmKernels() {
+  cudaError_t e = loadVariants<gemm::kEpiStore, gemm::kCommNone>();
+  if (e == cudaSuccess) e = loadVariants<gemm::kEpiSwiGLU, gemm::kCommNone>();
+  if (e == cudaSuccess) e = loadVariants<gemm::kEpiStore, gemm::kCommAllGather>();
+  if (e == cudaSuccess) e = loadVariants<gemm::kEpiSwiGLU, gemm::kCommAllGather>();
+  if (e == cudaSuccess) e = loadVariants<gemm::kEpiStore, gemm::kCommReduceScatter>();
+  if (e == cudaSuccess) {
+    static thread_local int last = -1;
+    static thread_local cudaError_t err = cudaSuccess;
+    e = ensureSmem(gemm::gemm2_bf16_kernel<gemm::kEpiStore, gemm::kCommReduceScatterCe>, &last, &err);
+  }
+  if (e != cudaSuccess) {
+    UCCL_LOG(ERROR, "loading the GEMM kernels failed: %s", cudaGetErrorString(e));
+    (void)cudaGetLastError();
+    return ucclSystemError;
+  }
+  (void)maxResidentPairs();
+  return ucclSuccess;
+}
 
 ucclResult_t launchGemmBf16(const GemmLaunch& g, const GemmFusion* f, cudaStream_t stream) {
   if (!g.A || !g.B || !g.C || g.M <= 0 || g.N <= 0 || g.K <= 0) return ucclInvalidArgument;

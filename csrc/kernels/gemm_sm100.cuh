@@ -27,7 +27,7 @@
 //       the stores have completed.  When its tiles are done every CTA helps to sum the n staged
 //       copies of this rank's own rows in fp32 (local loads only) into the output.  No SM is
 //       reserved for communication.  In the copy-engine variant the epilogue only writes local
-//       memory and counts finished chunks; side streams carry them (reduceScatterPushBegin).
+//       memory and counts finished chunks; side streams carry them (reduceScatterPushCopies).
 // Every TMA load writes only the shared memory of the CTA that issued it; peers' memory is
 // reached with plain (non-replicating) bulk copies.
 //
@@ -159,6 +159,7 @@ __device__ __forceinline__ bool wait_flag_geq(const uint32_t* flag, uint32_t tar
     return true;
   }
   const uint64_t t0 = ptx::globaltimer_ns();
+  const uint64_t limit = timeout_ns ? timeout_ns : 10000000000ull;  // never without a deadline
   uint32_t spins = 0, pause = 32;
   while (true) {
     if (ptx::ld_relaxed_sys_u32(flag) >= target) {
@@ -167,7 +168,7 @@ __device__ __forceinline__ bool wait_flag_geq(const uint32_t* flag, uint32_t tar
     }
     if ((++spins & 63u) == 0) {
       if (abort_flag && ptx::ld_relaxed_sys_u32(abort_flag)) return false;
-      if (timeout_ns && ptx::globaltimer_ns() - t0 > timeout_ns) return false;
+      if (ptx::globaltimer_ns() - t0 > limit) return false;
     }
     __nanosleep(pause);
     if (pause < 1024) pause <<= 1;

@@ -53,6 +53,12 @@ struct GemmFusion {
 
 ucclResult_t launchGemmBf16(const GemmLaunch& g, const GemmFusion* fusion, cudaStream_t stream);
 
+// Loads every GEMM kernel variant on the current device (once per thread and device).  CUDA loads
+// kernels lazily, and loading one may wait for the device to go idle: a caller that is about to
+// park side streams on stream memory operations that only the GEMM kernel can satisfy must have
+// the kernel loaded first, or the load would wait for those streams for ever.
+ucclResult_t preloadGemmKernels();
+
 // Number of SMs of the current device (cached per device).
 int deviceSmCount();
 

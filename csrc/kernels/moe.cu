@@ -88,7 +88,7 @@ __global__ void __launch_bounds__(kMoeThreads) moe_dispatch_kernel(const __grid_
     for (int k = 0; k < a.topk; ++k) {
       const int e = a.topkIdx[static_cast<size_t>(t) * a.topk + k];
       int slot = -1, dst = 0;
-      if (e >= 0) {
+      if (e >= 0 && e < a.numExperts) {
         dst = e / a.expertsPerRank;
         if (lane == 0) slot = static_cast<int>(atomicAdd(a.sendCount + dst, 1u));
         slot = __shfl_sync(0xffffffffu, slot, 0);

@@ -14,6 +14,7 @@ struct MoeArgs {
   int hidden;           // multiple of 128, at most 8192
   int topk;             // at most 16
   int expertsPerRank;
+  int numExperts;       // routing entries outside [0, numExperts) are unused slots
   int rowsPerSource;    // capacity of the region each source rank owns on every destination
   // symmetric receive area, one base pointer per rank
   char* recvX[UCCL_MAX_LOCAL_RANKS];       // fp8 [nranks][rowsPerSource][hidden]

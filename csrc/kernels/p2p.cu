@@ -1,7 +1,8 @@
 // Point-to-point send / receive over NVLink: the sender copies into slots of the receiver's
 // arena and bumps a tail counter there; the receiver drains the slots into the user's buffer and
 // bumps a head counter in the sender's arena.  One launch carries a whole group of operations;
-// every operation is striped over kP2pStripes CTAs, each with its own slice of the slots and its
+// operations with the same peer and direction share a FIFO and run one after the other as a
+// chain, different chains run side by side.  Every chain is striped over kP2pStripes CTAs, each with its own slice of the slots and its
 // own pair of counters, so eight copy loops run in parallel per direction.
 //
 // The reference lists send/recv as future work (desgin/design-spec.md:1760); its P2P transport
@@ -25,64 +26,67 @@ __device__ __forceinline__ char* slot_of(const DevComm& dc, int receiver, int se
 
 __global__ void __launch_bounds__(kThreads, 1) p2p_kernel(const __grid_constant__ P2pArgs a) {
   const DevComm& dc = a.dc;
-  const int opIdx = blockIdx.x / kP2pStripes, stripe = blockIdx.x % kP2pStripes;
-  if (opIdx >= a.nops) return;
-  const P2pOp& op = a.ops[opIdx];
-  // stripe split in 16-byte units; the last stripe carries the byte tail
-  size_t off, len;
-  {
-    size_t o, l;
-    split(op.bytes >> 4, kP2pStripes, stripe, &o, &l);
-    off = o << 4;
-    len = l << 4;
-    if (stripe == kP2pStripes - 1) len += op.bytes & 15;
-  }
-  if (len == 0) return;
+  const int chain = blockIdx.x / kP2pStripes, stripe = blockIdx.x % kP2pStripes;
+  if (chain >= a.nchains) return;
   __shared__ int s_ok;
-  P2pCtrl* mine = ctrl_of(dc, dc.rank, op.peer, stripe);
-  P2pCtrl* theirs = ctrl_of(dc, op.peer, dc.rank, stripe);
-  if (op.isSend) {
-    uint64_t sent = mine->sent;
+  const int first = a.heads[chain];
+  const int peer = a.ops[first].peer;
+  const bool isSend = a.ops[first].isSend != 0;
+  P2pCtrl* mine = ctrl_of(dc, dc.rank, peer, stripe);
+  P2pCtrl* theirs = ctrl_of(dc, peer, dc.rank, stripe);
+  // slots of this stripe's FIFO used so far; carried from one operation of the chain to the next
+  uint64_t pos = isSend ? mine->sent : mine->rcvd;
+  for (int oi = first; oi >= 0; oi = a.ops[oi].next) {
+    const P2pOp& op = a.ops[oi];
+    // stripe split in 16-byte units; the last stripe carries the byte tail
+    size_t off, len;
+    {
+      size_t o, l;
+      split(op.bytes >> 4, kP2pStripes, stripe, &o, &l);
+      off = o << 4;
+      len = l << 4;
+      if (stripe == kP2pStripes - 1) len += op.bytes & 15;
+    }
     for (size_t done = 0; done < len; done += kStripeSlotBytes) {
       const size_t n = min(kStripeSlotBytes, len - done);
-      if (threadIdx.x == 0)
-        s_ok = wait_u64(&mine->head, sent + 1 >= kP2pSlots ? sent + 1 - kP2pSlots : 0, dc, DEV_TIMEOUT_P2P, op.peer,
-                        static_cast<uint32_t>(sent));
-      __syncthreads();
-      if (!s_ok) return;
-      block_copy(slot_of(dc, op.peer, dc.rank, static_cast<int>(sent % kP2pSlots), stripe), op.src + off + done, n);
-      __syncthreads();
-      ++sent;
-      if (threadIdx.x == 0) {
-        ptx::fence_sys();
-        ptx::st_release_sys_u64(&theirs->tail, sent);
+      if (isSend) {
+        if (threadIdx.x == 0)
+          s_ok = wait_u64(&mine->head, pos + 1 >= kP2pSlots ? pos + 1 - kP2pSlots : 0, dc, DEV_TIMEOUT_P2P, peer,
+                          static_cast<uint32_t>(pos));
+        __syncthreads();
+        if (!s_ok) return;
+        block_copy(slot_of(dc, peer, dc.rank, static_cast<int>(pos % kP2pSlots), stripe), op.src + off + done, n);
+        __syncthreads();
+        ++pos;
+        if (threadIdx.x == 0) {
+          ptx::fence_sys();
+          ptx::st_release_sys_u64(&theirs->tail, pos);
+        }
+      } else {
+        if (threadIdx.x == 0) s_ok = wait_u64(&mine->tail, pos + 1, dc, DEV_TIMEOUT_P2P, peer, static_cast<uint32_t>(pos));
+        __syncthreads();
+        if (!s_ok) return;
+        block_copy(op.dst + off + done, slot_of(dc, dc.rank, peer, static_cast<int>(pos % kP2pSlots), stripe), n);
+        __syncthreads();
+        ++pos;
+        if (threadIdx.x == 0) {
+          ptx::fence_sys();
+          ptx::st_release_sys_u64(&theirs->head, pos);
+        }
       }
     }
-    if (threadIdx.x == 0) mine->sent = sent;
-  } else {
-    uint64_t rcvd = mine->rcvd;
-    for (size_t done = 0; done < len; done += kStripeSlotBytes) {
-      const size_t n = min(kStripeSlotBytes, len - done);
-      if (threadIdx.x == 0) s_ok = wait_u64(&mine->tail, rcvd + 1, dc, DEV_TIMEOUT_P2P, op.peer, static_cast<uint32_t>(rcvd));
-      __syncthreads();
-      if (!s_ok) return;
-      block_copy(op.dst + off + done, slot_of(dc, dc.rank, op.peer, static_cast<int>(rcvd % kP2pSlots), stripe), n);
-      __syncthreads();
-      ++rcvd;
-      if (threadIdx.x == 0) {
-        ptx::fence_sys();
-        ptx::st_release_sys_u64(&theirs->head, rcvd);
-      }
-    }
-    if (threadIdx.x == 0) mine->rcvd = rcvd;
+  }
+  if (threadIdx.x == 0) {
+    if (isSend) mine->sent = pos;
+    else mine->rcvd = pos;
   }
 }
 
 }  // namespace dev
 
 cudaError_t launchP2pKernel(const P2pArgs& a, cudaStream_t stream) {
-  if (a.nops < 1 || a.nops > kMaxP2pOps) return cudaErrorInvalidValue;
-  dev::p2p_kernel<<<a.nops * kP2pStripes, dev::kThreads, 0, stream>>>(a);
+  if (a.nchains < 1 || a.nchains > kMaxP2pChains) return cudaErrorInvalidValue;
+  dev::p2p_kernel<<<a.nchains * kP2pStripes, dev::kThreads, 0, stream>>>(a);
   return cudaGetLastError();
 }
 

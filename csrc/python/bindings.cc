@@ -13,7 +13,6 @@
 #include <vector>
 
 #include "uccl.h"
-#include "uccl_selftest.h"
 
 namespace py = pybind11;
 
@@ -48,8 +47,6 @@ ucclUniqueId idFromBytes(const py::bytes& b) {
 
 }  // namespace
 
-extern "C" ucclResult_t ucclUniqueIdFromAddress(const char* ip, int port, uint64_t seed, ucclUniqueId* id);
-extern "C" ucclResult_t ucclServeUniqueId(const ucclUniqueId* id);
 
 PYBIND11_MODULE(_uccl_bindings, m) {
   m.doc() = "Python bindings of the sm_100a unified collective library";
@@ -139,6 +136,17 @@ PYBIND11_MODULE(_uccl_bindings, m) {
         [](uintptr_t c, uintptr_t send, uintptr_t recv, size_t count, int dt, uintptr_t stream) {
           check(ucclAllReduce(P(send), P(recv), count, DT(dt), ucclSum, C(c), P(stream)), "ucclAllReduce", C(c));
         }, nogil());
+  m.def("allreduce_ex", [](uintptr_t c, uintptr_t send, uintptr_t recv, size_t count, int inType, int outType, float scale,
+                           uintptr_t scales, uintptr_t stream) {
+    check(ucclAllReduceEx(P(send), P(recv), count, DT(inType), DT(outType), scale, static_cast<float*>(P(scales)), C(c), P(stream)),
+          "ucclAllReduceEx", C(c));
+  }, nogil());
+  m.def("reduce_scatter_ex", [](uintptr_t c, uintptr_t send, uintptr_t recv, size_t recvcount, int inType, int outType,
+                                float scale, uintptr_t scales, uintptr_t stream) {
+    check(ucclReduceScatterEx(P(send), P(recv), recvcount, DT(inType), DT(outType), scale, static_cast<float*>(P(scales)), C(c),
+                              P(stream)),
+          "ucclReduceScatterEx", C(c));
+  }, nogil());
   m.def("allgather",
         [](uintptr_t c, uintptr_t send, uintptr_t recv, size_t sendcount, int dt, uintptr_t stream) {
           check(ucclAllGather(P(send), P(recv), sendcount, DT(dt), C(c), P(stream)), "ucclAllGather", C(c));
@@ -322,19 +330,4 @@ PYBIND11_MODULE(_uccl_bindings, m) {
     check(ucclWaitSignal(static_cast<int>(peers.size()), d, C(c), P(stream)), "ucclWaitSignal", C(c));
   }, nogil());
 
-  // ---------------------------------------------------------------- native self tests
-  m.def("selftest_names", [] {
-    std::vector<std::string> out;
-    for (int i = 0; i < ucclSelfTestCount(); ++i) out.push_back(ucclSelfTestName(i));
-    return out;
-  });
-  m.def("selftest_run", [](const std::string& name) {
-    std::vector<char> report(8192, 0);
-    int rc;
-    {
-      py::gil_scoped_release rel;
-      rc = ucclSelfTestRun(name.c_str(), report.data(), report.size());
-    }
-    return py::make_tuple(rc, std::string(report.data()));
-  });
 }

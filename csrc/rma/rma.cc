@@ -21,6 +21,7 @@ void closeWindow(Window* w) {
   Comm* c = w->comm;
   for (int p = 0; p < c->localRanks; ++p)
     if (w->ipcOpened[p] && w->ipcBase[p]) cudaIpcCloseMemHandle(w->ipcBase[p]);
+  if (w->dynTables) cudaFree(w->dynTables);
   w->magic = 0;
   delete w;
 }
@@ -348,5 +349,45 @@ extern "C" ucclResult_t ucclWindowGetDeviceHandle(ucclWindow_t win, ucclDeviceWi
     out->remotePtrs[p] = w->remotePtrs[p];
     out->remoteSignals[p] = reinterpret_cast<unsigned long long*>(w->remoteSignals[p]);
   }
+  return ucclSuccess;
+}
+
+// Pointer-table form of the descriptor (the reference's ucclDeviceWindowDyn,
+// src/rma/rma_device.hpp:61-70): the two per-peer tables are copied to device memory once per
+// window and freed with it.
+extern "C" ucclResult_t ucclWindowGetDeviceHandleDyn(ucclWindow_t win, ucclDeviceWindowDyn* out) {
+  Window* w = reinterpret_cast<Window*>(win);
+  if (!winValid(w) || !out) return ucclInvalidArgument;
+  Comm* c = w->comm;
+  DeviceGuard guard(c->cudaDev);
+  const int n = c->localRanks;
+  {
+    std::lock_guard<std::mutex> lk(c->winMu);
+    if (!w->dynTables) {
+      void* host[2 * UCCL_MAX_LOCAL_RANKS] = {};
+      for (int p = 0; p < n; ++p) {
+        host[p] = w->remotePtrs[p];
+        host[UCCL_MAX_LOCAL_RANKS + p] = w->remoteSignals[p];
+      }
+      void* d = nullptr;
+      if (cudaMalloc(&d, sizeof(host)) != cudaSuccess ||
+          cudaMemcpy(d, host, sizeof(host), cudaMemcpyHostToDevice) != cudaSuccess) {
+        if (d) cudaFree(d);
+        (void)cudaGetLastError();
+        commSetError(c, "no device memory for the window's pointer tables");
+        return ucclSystemError;
+      }
+      w->dynTables = d;
+    }
+  }
+  memset(out, 0, sizeof(*out));
+  out->localBuff = w->localBuff;
+  out->size = w->size;
+  out->nRanks = n;
+  out->myRank = c->localRank;
+  out->localSignals = reinterpret_cast<unsigned long long*>(w->localSignals);
+  out->timeoutNs = c->cfg.waitTimeoutMs * 1000000ull;
+  out->remotePtrs = static_cast<char**>(w->dynTables);
+  out->remoteSignals = reinterpret_cast<unsigned long long**>(static_cast<void**>(w->dynTables) + UCCL_MAX_LOCAL_RANKS);
   return ucclSuccess;
 }

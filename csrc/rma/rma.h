@@ -25,6 +25,7 @@ struct Window {
   char* ipcBase[UCCL_MAX_LOCAL_RANKS] = {};
   uint64_t* localSignals = nullptr;
   uint64_t* remoteSignals[UCCL_MAX_LOCAL_RANKS] = {};
+  void* dynTables = nullptr;  // device copy of remotePtrs | remoteSignals for ucclDeviceWindowDyn, made on demand
 };
 
 void rmaDestroyAll(Comm* c);

@@ -85,6 +85,11 @@ typedef struct ucclWindow* ucclWindow_t;
 ucclResult_t ucclGetVersion(int* version);
 /* Starts a rendezvous service in the calling process and encodes its address in the id. */
 ucclResult_t ucclGetUniqueId(ucclUniqueId* uniqueId);
+/* For launchers that already hand every rank a rendezvous address (MASTER_ADDR / MASTER_PORT):
+ * all ranks derive the same id from (ip, port, seed); exactly one of them also calls
+ * ucclServeUniqueId to run the rendezvous service there. */
+ucclResult_t ucclUniqueIdFromAddress(const char* ip, int port, uint64_t seed, ucclUniqueId* uniqueId);
+ucclResult_t ucclServeUniqueId(const ucclUniqueId* uniqueId);
 ucclResult_t ucclCommInitRank(ucclComm_t* comm, int nranks, ucclUniqueId commId, int rank);
 /* One process, ndev communicators (one per entry of devlist, or devices 0..ndev-1). */
 ucclResult_t ucclCommInitAll(ucclComm_t* comm, int ndev, const int* devlist);
@@ -104,6 +109,20 @@ ucclResult_t ucclAllGather(const void* sendbuff, void* recvbuff, size_t sendcoun
 ucclResult_t ucclReduceScatter(const void* sendbuff, void* recvbuff, size_t recvcount,
                                ucclDataType_t datatype, ucclRedOp_t op, ucclComm_t comm,
                                void* stream);
+
+/* ------------------------------------------------------------------ collectives with a fused epilogue
+ * out = cast<outType>(scale * sum over ranks(in)): the sum is carried in fp32 from the peer loads
+ * to the store, so scaling and changing the element type cost no extra pass over memory.
+ * inType: fp16 / bf16 / fp32.  outType: fp16 / bf16 / fp32, or fp8-e4m3, in which case every 128
+ * consecutive elements share one fp32 scale (amax / 448) written to blockScales.
+ * Buffers are 16-byte aligned; recvcount (count / nranks for the all-reduce) is a multiple of one
+ * 16-byte input vector, of 128 for fp8 output.  Not deferrable into a group. */
+ucclResult_t ucclReduceScatterEx(const void* sendbuff, void* recvbuff, size_t recvcount,
+                                 ucclDataType_t inType, ucclDataType_t outType, float scale,
+                                 float* blockScales, ucclComm_t comm, void* stream);
+ucclResult_t ucclAllReduceEx(const void* sendbuff, void* recvbuff, size_t count, ucclDataType_t inType,
+                             ucclDataType_t outType, float scale, float* blockScales, ucclComm_t comm,
+                             void* stream);
 
 /* ------------------------------------------------------------------ group */
 ucclResult_t ucclGroupStart(void);

@@ -16,15 +16,15 @@
 #include <thread>
 #include <vector>
 
-#include "../host/host_coll.h"
-#include "../host/ring_schedule.h"
-#include "../protocols/protocol.h"
-#include "../transport/net_plugin.h"
-#include "bootstrap.h"
-#include "comm.h"
-#include "config.h"
-#include "topo.h"
-#include "tuner.h"
+#include "host/host_coll.h"
+#include "host/ring_schedule.h"
+#include "protocols/protocol.h"
+#include "transport/net_plugin.h"
+#include "core/bootstrap.h"
+#include "core/comm.h"
+#include "core/config.h"
+#include "core/topo.h"
+#include "core/tuner.h"
 
 namespace uccl {
 namespace {
@@ -597,6 +597,14 @@ std::string testConfig() {
   EXPECT(c.waitTimeoutMs == 1500);
   Config d = loadConfig();
   EXPECT(d.algo == ucclAlgoAuto && d.execMode == EXEC_SM_ONLY && !d.forceNet && d.waitTimeoutMs == 10000);
+  // a wait budget of zero, a negative one or an absurd one is clamped: device waits stay bounded
+  setenv("UCCL_WAIT_TIMEOUT_MS", "0", 1);
+  EXPECT(loadConfig().waitTimeoutMs == 1);
+  setenv("UCCL_WAIT_TIMEOUT_MS", "-5", 1);
+  EXPECT(loadConfig().waitTimeoutMs == 1);
+  setenv("UCCL_WAIT_TIMEOUT_MS", "99999999999", 1);
+  EXPECT(loadConfig().waitTimeoutMs == 600000);
+  unsetenv("UCCL_WAIT_TIMEOUT_MS");
   return "";
 }
 
@@ -730,12 +738,4 @@ extern "C" int ucclSelfTestRun(const char* name, char* report, size_t reportLen)
   }
   if (report && reportLen) snprintf(report, reportLen, "no such self test: %s", name);
   return 2;
-}
-
-extern "C" ucclResult_t ucclUniqueIdFromAddress(const char* ip, int port, uint64_t seed, ucclUniqueId* id) {
-  return uccl::bootstrapIdFromAddress(ip, port, seed, id);
-}
-extern "C" ucclResult_t ucclServeUniqueId(const ucclUniqueId* id) {
-  if (!id) return ucclInvalidArgument;
-  return uccl::bootstrapServeId(*id, uccl::loadConfig());
 }

@@ -175,6 +175,119 @@ def case_allreduce_algos(comm, rank, n, args):
     return {"fail": fail, "algo_hist": comm.counters()["algo_hist"], "nvls": comm.info["nvls"]}
 
 
+def case_ring_ce_matrix(comm, rank, n, args):
+    """All-gather, reduce-scatter and all-reduce forced onto the ring (Simple and LL128) and onto the
+    copy engines, out of place and in place.  Run with a small UCCL_STAGING_BYTES and few CTAs so that
+    one chunk needs more pieces than a channel has slots (several rounds of the reduce-scatter
+    schedule, FIFO wrap-around) and the copy-engine path loops over its staging area."""
+    dev = _dev(comm, rank)
+    fail = []
+    combos = [("ring", "simple"), ("ring", "ll128"), ("copy_engine", "simple")]
+    for dt in (torch.float32, torch.bfloat16):
+        tol = {torch.float32: 1e-5, torch.bfloat16: 2e-2}[dt] * n
+        for cnt in (5, 4099, (1 << 20) + 3):
+            mine = _seeded(cnt, 300 + rank, dt)
+            full = [_seeded(cnt * n, 99 + p, dt) for p in range(n)]
+            exp_ag = torch.cat([_seeded(cnt, 300 + p, dt) for p in range(n)])
+            exp_rs = sum(f.float() for f in full)[rank * cnt:(rank + 1) * cnt]
+            exp_ar = sum(_seeded(cnt, 300 + p, dt).float() for p in range(n))
+            for algo, proto in combos:
+                if proto == "ll128" and cnt > (1 << 18):
+                    continue  # 112 payload bytes per 128-byte line: keep the slow protocol to small messages
+                comm.set_algo(algo, proto)
+                # all-gather, out of place then in place (my part already sits in the output)
+                r = torch.zeros(cnt * n, dtype=dt, device=dev)
+                comm.allgather(mine.to(dev), r)
+                _sync(comm)
+                if not torch.equal(r.cpu(), exp_ag):
+                    fail.append(("allgather", algo, proto, str(dt), cnt))
+                r2 = torch.zeros(cnt * n, dtype=dt, device=dev)
+                r2[rank * cnt:(rank + 1) * cnt] = mine.to(dev)
+                comm.allgather(r2[rank * cnt:(rank + 1) * cnt], r2)
+                _sync(comm)
+                if not torch.equal(r2.cpu(), exp_ag):
+                    fail.append(("allgather_inplace", algo, proto, str(dt), cnt))
+                # reduce-scatter, out of place then in place (output = my part of the input)
+                s2 = full[rank].to(dev)
+                o = torch.zeros(cnt, dtype=dt, device=dev)
+                comm.reduce_scatter(s2, o)
+                _sync(comm)
+                e = (o.float().cpu() - exp_rs).abs().max().item()
+                if e > tol:
+                    fail.append(("reduce_scatter", algo, proto, str(dt), cnt, e))
+                s3 = full[rank].to(dev)
+                comm.reduce_scatter(s3, s3[rank * cnt:(rank + 1) * cnt])
+                _sync(comm)
+                e = (s3[rank * cnt:(rank + 1) * cnt].float().cpu() - exp_rs).abs().max().item()
+                if e > tol:
+                    fail.append(("reduce_scatter_inplace", algo, proto, str(dt), cnt, e))
+                x = mine.to(dev)
+                comm.allreduce(x)
+                _sync(comm)
+                e = (x.float().cpu() - exp_ar).abs().max().item()
+                if e > tol:
+                    fail.append(("allreduce", algo, proto, str(dt), cnt, e))
+    comm.set_algo("auto", "auto")
+    return {"fail": fail, "algo_hist": comm.counters()["algo_hist"]}
+
+
+def case_fused_cast(comm, rank, n, args):
+    """Reduce-scatter / all-reduce with scale and a different output type against the fp32 restatement:
+    bf16 -> fp32, bf16 -> bf16, fp32 -> bf16, fp16 -> fp16, and bf16 / fp32 -> fp8-e4m3 with 1 x 128 scales;
+    symmetric and ordinary input buffers (the latter in several staged pieces)."""
+    from unified_ccl_b200.parallel import quantize_fp8_block128
+
+    dev = _dev(comm, rank)
+    fail = []
+    f8 = torch.float8_e4m3fn
+    pairs = [(torch.bfloat16, torch.float32), (torch.bfloat16, torch.bfloat16), (torch.float32, torch.bfloat16),
+             (torch.float16, torch.float16), (torch.bfloat16, f8), (torch.float32, f8)]
+    for per in (128, 5 * 128, 3 * 4096 + 128, 1 << 19):
+        for din, dout in pairs:
+            for sym in (True, False):
+                scale = 0.37
+                full = [_seeded(per * n, 700 + p, din) for p in range(n)]
+                tot = sum(f.float() for f in full) * scale
+                exp = tot[rank * per:(rank + 1) * per]
+                s_in = comm.empty(per * n, din) if sym else torch.empty(per * n, dtype=din, device=dev)
+                s_in.copy_(full[rank])
+                out = torch.empty(per, dtype=dout, device=dev)
+                out, scales = comm.reduce_scatter_cast(s_in, out, scale)
+                _sync(comm)
+                if dout == f8:
+                    q, sc = quantize_fp8_block128(exp.view(1, -1))
+                    deq = out.float().cpu().view(-1, 128) * scales.cpu().view(-1, 1)
+                    ref = q.float().view(-1, 128) * sc.view(-1, 1)
+                    # a sum that differs in the last fp32 bit can move an element across one fp8 step
+                    amax = exp.view(-1, 128).abs().amax(-1, keepdim=True)
+                    bad = ((deq - ref).abs() > 0.0625 * amax + 1e-6).sum().item()
+                    if bad or not torch.allclose(scales.cpu(), sc.view(-1), rtol=1e-5, atol=0):
+                        fail.append(("rs_fp8", str(din), per, sym, bad))
+                else:
+                    tol = {torch.float32: 2e-6, torch.bfloat16: 8e-3, torch.float16: 1e-3}[dout] * max(1.0, exp.abs().max().item())
+                    e = (out.float().cpu() - exp).abs().max().item()
+                    if e > tol:
+                        fail.append(("rs_cast", str(din), str(dout), per, sym, e))
+                # all-reduce form on the same data
+                o2 = torch.empty(per * n, dtype=dout, device=dev)
+                o2, sc2 = comm.allreduce_cast(s_in, o2, scale)
+                _sync(comm)
+                if dout == f8:
+                    deq = o2.float().cpu().view(-1, 128) * sc2.cpu().view(-1, 1)
+                    amax = tot.view(-1, 128).abs().amax(-1, keepdim=True)
+                    bad = ((deq - tot.view(-1, 128)).abs() > 0.07 * amax + 1e-6).sum().item()
+                    if bad:
+                        fail.append(("ar_fp8", str(din), per, sym, bad))
+                else:
+                    tol = {torch.float32: 2e-6, torch.bfloat16: 8e-3, torch.float16: 1e-3}[dout] * max(1.0, tot.abs().max().item())
+                    e = (o2.float().cpu() - tot).abs().max().item()
+                    if e > tol:
+                        fail.append(("ar_cast", str(din), str(dout), per, sym, e))
+                if sym:
+                    comm.free(s_in)
+    return {"fail": fail}
+
+
 def case_sendrecv(comm, rank, n, args):
     dev = _dev(comm, rank)
     fail = []
@@ -201,6 +314,21 @@ def case_sendrecv(comm, rank, n, args):
         _sync(comm)
         if not torch.equal(r.cpu(), torch.arange(1000, dtype=torch.float32) + peer):
             fail.append(("pair",))
+    # two sends and two receives with the same peer in one group share a FIFO and keep their order;
+    # a long group (more operations per peer than one launch carries) is cut at the same places on both ends
+    for reps, cnt in ((2, 3000), (2, (3 << 20) + 5), (5, 70001)):
+        nxt, prv = (rank + 1) % n, (rank - 1) % n
+        ss = [torch.full((cnt + i,), float(10 * rank + i), device=dev) for i in range(reps)]
+        rr = [torch.empty(cnt + i, device=dev) for i in range(reps)]
+        with comm.group():
+            for i in range(reps):
+                comm.send(ss[i], nxt)
+            for i in range(reps):
+                comm.recv(rr[i], prv)
+        _sync(comm)
+        for i in range(reps):
+            if not (rr[i].cpu() == 10 * prv + i).all():
+                fail.append(("same_peer_twice", reps, cnt, i))
     # send to self inside a group
     s = torch.full((64,), 7.0, device=dev)
     r = torch.zeros(64, device=dev)
@@ -390,6 +518,127 @@ def case_rma(comm, rank, n, args):
     return {"fail": fail}
 
 
+def case_rma_device(comm, rank, n, args):
+    """Kernels that call the device-side one-sided API (include/uccl_device.cuh) between GPUs:
+    put + signal, cooperative / multi waits, element put / get, get + signal, fused get + reduce for
+    fp32 / bf16 / fp16, both descriptor forms, and a wait that runs out (a signal nobody sends)."""
+    import ctypes
+
+    from unified_ccl_b200 import Window
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    lib = ctypes.CDLL(os.path.join(root, "tests", "native", "libuccl_devtest.so"))
+    vp, sz, u64, ci = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_ulonglong, ctypes.c_int
+    lib.ucclDevTestPutSignal.argtypes = [vp, ci, ci, sz, vp, sz, vp]
+    lib.ucclDevTestWaitReduce.argtypes = [vp, ci, ci, u64, ci, vp, vp, sz, sz, vp, vp]
+    lib.ucclDevTestWaitMultiGet.argtypes = [vp, vp, vp, ci, sz, vp, sz, vp, vp]
+    lib.ucclDevTestPutElements.argtypes = [vp, ci, sz, vp, sz, vp]
+    lib.ucclDevTestGetElements.argtypes = [vp, ci, sz, vp, sz, vp]
+    lib.ucclDevTestMakeWindow.argtypes = [vp]
+    dev = _dev(comm, rank)
+    fail = []
+    nxt, prv = (rank + 1) % n, (rank - 1) % n
+    stream = comm._stream()
+    dts = {torch.float32: 2, torch.bfloat16: 1, torch.float16: 0}
+
+    def barrier():
+        comm.allreduce(torch.zeros(1, device=dev))
+        _sync(comm)
+
+    for dyn in (0, 1):
+        cnt = 1 << 14
+        buf = comm.empty(cnt, torch.float32)
+        buf.zero_()
+        buf[: cnt // 4] = float(rank + 1)  # what my successor pulls and reduces
+        _sync(comm)
+        win = Window(comm, buf)
+        if lib.ucclDevTestMakeWindow(win._win) != 0:
+            fail.append(("makeDeviceWindow", dyn))
+        ok = torch.zeros(1, dtype=torch.int32, device=dev)
+        seen = {p: 0 for p in range(n)}  # signals received from each peer so far
+        for it in range(1, 4):
+            src = torch.full((cnt // 2,), float(100 * it + rank), device=dev)
+            rc = lib.ucclDevTestPutSignal(win._win, dyn, nxt, (cnt // 4) * 4, src.data_ptr(), src.numel() * 4, stream)
+            seen[prv] += 1
+            ones = torch.ones(cnt // 4, device=dev)
+            res = torch.empty(cnt // 4, device=dev)
+            rc |= lib.ucclDevTestWaitReduce(win._win, dyn, prv, seen[prv], dts[torch.float32], ones.data_ptr(), res.data_ptr(),
+                                            cnt // 4, 0, ok.data_ptr(), stream)
+            _sync(comm)
+            if rc != 0 or ok.item() != 1:
+                fail.append(("launch/wait", dyn, it, rc, ok.item()))
+                break
+            if not (buf[cnt // 4: cnt // 4 + cnt // 2] == 100 * it + prv).all().item():
+                fail.append(("put_signal", dyn, it))
+            if not (res == prv + 2).all().item():
+                fail.append(("get_reduce_f32", dyn, it))
+            barrier()
+        # 16-bit get + reduce: widened to fp32, rounded once
+        for dt in (torch.bfloat16, torch.float16):
+            w16 = comm.empty(4096, dt)
+            w16.copy_(_seeded(4096, 40 + rank, dt))
+            _sync(comm)
+            win16 = Window(comm, w16)
+            barrier()
+            loc = _seeded(4096, 80 + rank, dt).to(dev)
+            out = torch.empty_like(loc)
+            rc = lib.ucclDevTestWaitReduce(win16._win, dyn, prv, 0, dts[dt], loc.data_ptr(), out.data_ptr(), 4096, 0,
+                                           ok.data_ptr(), stream)
+            _sync(comm)
+            exp = (loc.float().cpu() + _seeded(4096, 40 + prv, dt).float()).to(dt)
+            if rc != 0 or ok.item() != 1 or not torch.equal(out.cpu(), exp):
+                fail.append(("get_reduce", str(dt), dyn, rc))
+            barrier()
+            win16.close()
+            comm.free(w16)
+        if dyn == 0:
+            # element put in both directions, one multi wait for both neighbours, then get + signal
+            buf.zero_()
+            barrier()
+            a = torch.full((64,), float(1000 + rank), device=dev)
+            rc = lib.ucclDevTestPutElements(win._win, nxt, 0, a.data_ptr(), 64, stream)
+            rc |= lib.ucclDevTestPutElements(win._win, prv, 64, a.data_ptr(), 64, stream)
+            seen[prv] += 1
+            seen[nxt] += 1
+            peers = sorted({prv, nxt})
+            pd = torch.tensor(peers, dtype=torch.int32, device=dev)
+            ed = torch.tensor([seen[p] for p in peers], dtype=torch.int64, device=dev)
+            got = torch.zeros(128, device=dev)
+            barrier()  # every window is filled before anybody pulls from one
+            rc |= lib.ucclDevTestWaitMultiGet(win._win, pd.data_ptr(), ed.data_ptr(), len(peers), 0, got.data_ptr(), 128 * 4,
+                                              ok.data_ptr(), stream)
+            seen[peers[0]] += 1  # deviceGetSignal counts the pull on the local counter of that peer
+            _sync(comm)
+            if rc != 0 or ok.item() != 1:
+                fail.append(("multi", rc, ok.item()))
+            if not ((buf[:64] == 1000 + prv).all().item() and (buf[64:128] == 1000 + nxt).all().item()):
+                fail.append(("put_elements",))
+            # what peers[0] holds in its first 128 floats: [1000 + its prv] * 64 + [1000 + its nxt] * 64
+            q = peers[0]
+            expq = torch.cat([torch.full((64,), 1000.0 + (q - 1) % n), torch.full((64,), 1000.0 + (q + 1) % n)])
+            if not torch.equal(got.cpu(), expq):
+                fail.append(("get_signal",))
+            g2 = torch.zeros(64, device=dev)
+            rc = lib.ucclDevTestGetElements(win._win, nxt, 64, g2.data_ptr(), 64, stream)
+            _sync(comm)
+            if rc != 0 or not (g2 == 1000 + (nxt + 1) % n).all().item():
+                fail.append(("get_elements", rc))
+            # a wait that runs out: nobody sends this signal; the kernel reports it and returns
+            t0 = time.time()
+            rc = lib.ucclDevTestWaitReduce(win._win, dyn, prv, 10 ** 9, dts[torch.float32], 0, 0, 0, 0, ok.data_ptr(), stream)
+            _sync(comm)
+            took = time.time() - t0
+            if rc != 0 or ok.item() != 0 or took > 20:
+                fail.append(("timeout path", rc, ok.item(), took))
+            z = torch.ones(8, device=dev) * 2
+            if z.sum().item() != 16:
+                fail.append(("context unusable",))
+        barrier()
+        win.close()
+        comm.free(buf)
+    return {"fail": fail}
+
+
 def case_moe(comm, rank, n, args):
     from unified_ccl_b200.parallel import MoeDispatcher, quantize_fp8_block128
 
@@ -517,6 +766,11 @@ def case_peer_exits(comm, rank, n, args):
 
 def main():
     case, rank, n, idfile = sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), sys.argv[4]
+    if os.environ.get("UCCL_TEST_DUMP_AFTER_S"):
+        # a rank that is still running after this many seconds prints where it is and exits
+        import faulthandler
+
+        faulthandler.dump_traceback_later(float(os.environ["UCCL_TEST_DUMP_AFTER_S"]), exit=True)
     args = sys.argv[5:]
     res = {"rank": rank}
     comm = None

@@ -35,12 +35,32 @@ def test_allreduce_every_algorithm():
         assert hist[4] > 0
 
 
+def test_ring_and_copy_engine_allgather_reduce_scatter():
+    """Ring (Simple, LL128) and copy-engine all-gather / reduce-scatter / all-reduce with a staging area so
+    small that a chunk needs more pieces than a channel has slots."""
+    env = {"UCCL_STAGING_BYTES": "1M", "UCCL_MAX_CTAS": "2", "UCCL_WAIT_TIMEOUT_MS": "5000"}
+    res = run_ranks("ring_ce_matrix", _n(), env=env, timeout=300)
+    assert_all_ok(res)
+    assert res[0]["algo_hist"][1] > 0 and res[0]["algo_hist"][5] > 0
+
+
+def test_collectives_with_scale_and_cast():
+    """ucclReduceScatterEx / ucclAllReduceEx: sum, scale, other output type (fp32 / bf16 / fp16 / fp8 + scales)."""
+    env = {"UCCL_STAGING_BYTES": "4M"}
+    assert_all_ok(run_ranks("fused_cast", _n(), env=env, timeout=300))
+
+
 def test_sendrecv():
     assert_all_ok(run_ranks("sendrecv", _n()))
 
 
 def test_rma_put_get_signal():
     assert_all_ok(run_ranks("rma", _n()))
+
+
+def test_rma_device_api():
+    """devicePutSignal / deviceWaitSignal* / deviceGetReduce<T> ... called from kernels, 2 or more GPUs."""
+    assert_all_ok(run_ranks("rma_device", min(_n(), 4), env={"UCCL_WAIT_TIMEOUT_MS": "800"}))
 
 
 def test_fused_allreduce_residual_rmsnorm():

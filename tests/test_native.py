@@ -1,12 +1,25 @@
-"""Native (C++) unit tests of the host runtime, one pytest case per self test."""
+"""Native (C++) unit tests of the host runtime, one pytest case per self test.  The tests live in
+tests/native/selftest.cc and are built into tests/native/libuccl_selftest.so (test-only code, not
+part of libuccl.so); this file drives them through ctypes."""
+import ctypes
 import os
 
 import pytest
 
 import unified_ccl_b200 as u
 
-NAMES = u._C.selftest_names()
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+_LIB = ctypes.CDLL(os.path.join(ROOT, "tests", "native", "libuccl_selftest.so"))
+_LIB.ucclSelfTestName.restype = ctypes.c_char_p
+_LIB.ucclSelfTestName.argtypes = [ctypes.c_int]
+_LIB.ucclSelfTestRun.argtypes = [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_size_t]
+NAMES = [_LIB.ucclSelfTestName(i).decode() for i in range(_LIB.ucclSelfTestCount())]
+
+
+def _run(name):
+    report = ctypes.create_string_buffer(8192)
+    rc = _LIB.ucclSelfTestRun(name.encode(), report, len(report))
+    return rc, report.value.decode(errors="replace")
 
 
 def test_selftests_exist():
@@ -19,12 +32,12 @@ def test_selftest(name, monkeypatch):
     plugin = os.path.join(ROOT, "plugins", "sample", "libuccl-net-sample.so")
     if os.path.exists(plugin):
         monkeypatch.setenv("UCCL_SELFTEST_PLUGIN", plugin)
-    rc, report = u._C.selftest_run(name)
+    rc, report = _run(name)
     assert rc == 0, report
 
 
 def test_unknown_selftest():
-    rc, report = u._C.selftest_run("does_not_exist")
+    rc, report = _run("does_not_exist")
     assert rc == 2 and "no such" in report
 
 

@@ -174,6 +174,42 @@ class Communicator:
                           _DTYPES[send_tensor.dtype], self._stream())
         return recv_tensor
 
+    def _ex_args(self, send_tensor, out_tensor, scales, per_rank):
+        self._check(send_tensor, reducible=True)
+        self._check(out_tensor)
+        if out_tensor.dtype not in _REDUCIBLE and _DTYPES[out_tensor.dtype] != 3:
+            raise TypeError("output must be float16, bfloat16, float32 or float8_e4m3fn")
+        if _DTYPES[out_tensor.dtype] == 3:
+            if scales is None:
+                scales = torch.empty(out_tensor.numel() // 128, dtype=torch.float32, device=out_tensor.device)
+            if scales.dtype != torch.float32 or scales.numel() * 128 != out_tensor.numel() or per_rank % 128:
+                raise ValueError("fp8 output takes one float32 scale per 128 elements")
+        else:
+            scales = None
+        return scales
+
+    def reduce_scatter_cast(self, send_tensor: torch.Tensor, recv_tensor: torch.Tensor, scale: float = 1.0,
+                            scales: torch.Tensor = None):
+        """``recv = cast(scale * reduce_scatter(send))`` in one kernel: the sum stays in fp32 until the
+        store.  ``recv_tensor`` may be float16 / bfloat16 / float32, or float8_e4m3fn with one float32
+        scale per 128 elements (returned as the second value)."""
+        if send_tensor.numel() != recv_tensor.numel() * self._world_size:
+            raise ValueError("send_tensor must hold world_size * recv_tensor.numel() elements")
+        scales = self._ex_args(send_tensor, recv_tensor, scales, recv_tensor.numel())
+        _C.reduce_scatter_ex(self._comm, send_tensor.data_ptr(), recv_tensor.data_ptr(), recv_tensor.numel(),
+                             _DTYPES[send_tensor.dtype], _DTYPES[recv_tensor.dtype], float(scale),
+                             scales.data_ptr() if scales is not None else 0, self._stream())
+        return recv_tensor, scales
+
+    def allreduce_cast(self, send_tensor: torch.Tensor, out: torch.Tensor, scale: float = 1.0, scales: torch.Tensor = None):
+        """``out = cast(scale * allreduce(send))``; the gather half moves elements of the output type."""
+        if send_tensor.numel() != out.numel():
+            raise ValueError("out must hold as many elements as send_tensor")
+        scales = self._ex_args(send_tensor, out, scales, out.numel() // self._world_size)
+        _C.allreduce_ex(self._comm, send_tensor.data_ptr(), out.data_ptr(), send_tensor.numel(), _DTYPES[send_tensor.dtype],
+                        _DTYPES[out.dtype], float(scale), scales.data_ptr() if scales is not None else 0, self._stream())
+        return out, scales
+
     def broadcast(self, tensor: torch.Tensor, root: int = 0) -> torch.Tensor:
         self._check(tensor)
         if not 0 <= root < self._world_size:
