@@ -59,9 +59,11 @@ UCXPLUGIN := plugins/ucx/libuccl-net-ucx.so
 SELFTEST  := tests/native/libuccl_selftest.so
 DEVTEST   := tests/native/libuccl_devtest.so
 CLIENT    := tests/native/c_api_client
+# one-pass SwiGLU of the NCCL + cuBLAS comparator (bench.py); not part of the library
+BASELINE  := baseline/libbaseline_swiglu.so
 PUBLIC_HEADERS := include/uccl.h include/uccl_net.h include/uccl_device.cuh include/uccl_noalloc.h
 
-TARGETS := $(LIB)
+TARGETS := $(LIB) $(BASELINE)
 ifeq ($(UCCL_BUILD_PYTHON),1)
 TARGETS += $(PYMOD)
 endif
@@ -110,6 +112,9 @@ $(SELFTEST): tests/native/selftest.cc tests/native/uccl_selftest.h $(LIB) $(wild
 $(DEVTEST): tests/native/rma_device_test.cu include/uccl_device.cuh include/uccl.h $(LIB)
 	$(NVCC) $(NVFLAGS) -shared $< -o $@ -L$(PKG) -luccl -Xlinker -rpath,'$$ORIGIN/../../$(PKG)' -lcudart_static
 
+$(BASELINE): baseline/swiglu_kernel.cu
+	$(NVCC) $(NVFLAGS) -shared $< -o $@ -lcudart_static
+
 $(CLIENT): tests/native/c_api_client.cc include/uccl.h $(LIB)
 	$(CXX) $(CXXFLAGS) $< -o $@ -L$(PKG) -luccl -Wl,-rpath,'$$ORIGIN/../../$(PKG)' -L$(CUDA_HOME)/lib64 -lcudart_static -ldl -lpthread -lrt
 
@@ -142,6 +147,6 @@ $(eval $(call SAN_RULES,asan))
 $(eval $(call SAN_RULES,tsan))
 
 clean:
-	rm -rf $(BUILD) $(LIB) $(PYMOD) $(PLUGIN) $(SELFTEST) $(DEVTEST) $(CLIENT) plugins/ucx/*.so
+	rm -rf $(BUILD) $(LIB) $(PYMOD) $(PLUGIN) $(SELFTEST) $(DEVTEST) $(CLIENT) $(BASELINE) plugins/ucx/*.so
 
 .PHONY: all clean asan tsan install ucx-fake

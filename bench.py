@@ -71,6 +71,7 @@ def main():
     rows = tokens // world
     mlp = TensorParallelMLP(comm, HIDDEN, FFN, tokens, seed=0)
     base = NcclCublasMLP(mlp.w_gate_up, mlp.w_down, tokens, world)
+    base_fused = NcclCublasMLP(mlp.w_gate_up, mlp.w_down, tokens, world, fused_swiglu=True)  # one-pass SwiGLU: the stronger comparator
     autotune = {}
     autotune_rs = {}
     g = torch.Generator(device="cpu").manual_seed(1234 + rank)
@@ -80,8 +81,8 @@ def main():
     if world > 1 and not os.environ.get("UCCL_FUSED_AG"):
         autotune = {"%s/ctas%d/chunks%d" % k: v for k, v in mlp.autotune(x_dev).items()}
         autotune["chosen"] = "%s/ctas%d/chunks%d" % mlp.ag_choice
-    # the copy-engine reduce-scatter has not been run on GPUs yet: its tuning pass is opt-in
-    if world > 1 and os.environ.get("UCCL_BENCH_TUNE_RS") and not os.environ.get("UCCL_FUSED_RS"):
+    # untimed: the same for the GEMM -> reduce-scatter half (epilogue stores or copy engines)
+    if world > 1 and not os.environ.get("UCCL_FUSED_RS"):
         mlp(x_dev)  # fills the activations the second half works on
         autotune_rs = {"%s/chunks%d" % k: v for k, v in mlp.autotune_rs().items()}
         autotune_rs["chosen"] = "%s/chunks%d" % mlp.rs_choice
@@ -116,6 +117,7 @@ def main():
         ms_ours = timed(lambda: mlp(x_dev), args.steps, args.warmup)
     clocks = clk.summary()
     ms_base = timed(lambda: base(x_dev), args.steps, args.warmup)
+    ms_base_fused = timed(lambda: base_fused(x_dev), args.steps, args.warmup)
 
     # ---- end to end through the public API: H2D of the step's input, D2H of a checksum
     x_in = torch.empty_like(x_dev)
@@ -128,6 +130,7 @@ def main():
 
     ms_e2e = timed(lambda: e2e_step(mlp), args.steps, args.warmup)
     ms_e2e_base = timed(lambda: e2e_step(base), args.steps, args.warmup)
+    ms_e2e_base_fused = timed(lambda: e2e_step(base_fused), args.steps, args.warmup)
 
     # ---- correctness spot check against the fp32 restatement (outside the timed regions)
     y = mlp(x_dev).float()
@@ -192,6 +195,8 @@ def main():
                        "l2": "per-rank working set (weights + activations + scratch) exceeds the 126 MB L2; no flush"},
             "nccl_cublas_us": round(ms_base * 1e3, 2),
             "speedup_vs_nccl_cublas": round(ms_base / ms_ours, 3),
+            "nccl_cublas_fused_swiglu_us": round(ms_base_fused * 1e3, 2),
+            "speedup_vs_nccl_cublas_fused_swiglu": round(ms_base_fused / ms_ours, 3),
             "tokens_per_s": round(tokens / (ms_ours * 1e-3), 1),
             "roofline_us": round(roof_us, 1),
             "fraction_of_roofline": round(roof_us / (ms_ours * 1e3), 3),
@@ -199,7 +204,8 @@ def main():
             "max_rel_diff_vs_nccl_cublas": round(rel, 5),
             "clocks": clocks,
             "e2e": {"value": round(ms_e2e * 1e3, 2), "unit": "us", "h2d_bytes_per_step": x_host.numel() * 2,
-                    "d2h_bytes_per_step": 4, "nccl_cublas_value": round(ms_e2e_base * 1e3, 2)},
+                    "d2h_bytes_per_step": 4, "nccl_cublas_value": round(ms_e2e_base * 1e3, 2),
+                    "nccl_cublas_fused_swiglu_value": round(ms_e2e_base_fused * 1e3, 2)},
             "gpu_launches": launches_per_step * args.steps,
             "allreduce_vs_nccl": sweep,
             "comm": {k: comm.info[k] for k in ("nvls", "p2p_mode", "net_active")},

@@ -100,6 +100,10 @@ def main():
                 os.environ["UCCL_NORM_DEBUG"] = str(bits)
                 parts[name] = round(timed(lambda: allreduce_residual_rmsnorm(comm, x, res, gamma, 1e-6, out=out, residual_out=res)), 1)
             os.environ["UCCL_NORM_DEBUG"] = "0"
+            for rows in (1, 2, 4):  # rows per pass of phase A on the switch path
+                os.environ["UCCL_NORM_MC_ROWS"] = str(rows)
+                parts["mc_rows_%d" % rows] = round(timed(lambda: allreduce_residual_rmsnorm(comm, x, res, gamma, 1e-6, out=out, residual_out=res)), 1)
+            os.environ.pop("UCCL_NORM_MC_ROWS", None)
             for algo in ("nvls", "two_shot"):
                 if algo == "nvls" and not comm.info["nvls"]:
                     continue

@@ -34,10 +34,13 @@ def main():
     ap.add_argument("--colls", default="allreduce,allgather,reducescatter,broadcast,sendrecv,alltoall")
     ap.add_argument("--dtypes", default="bf16")
     ap.add_argument("--unregistered", action="store_true", help="also time ordinary (non-symmetric) buffers")
-    ap.add_argument("--blocks", default="", help="comma list of CTA counts to try per algorithm (default: tuner's)")
+    ap.add_argument("--blocks", default="", help="comma list of CTA counts to try besides the tuner's (two-shot / NVLS, from 256 KiB up)")
+    ap.add_argument("--no-table", action="store_true", help="measure with the built-in priors (UCCL_TUNE_AUTO=0)")
     args = ap.parse_args()
 
     os.environ.setdefault("UCCL_BOOTSTRAP_IFNAME", "lo")
+    if args.no_table:
+        os.environ["UCCL_TUNE_AUTO"] = "0"
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -89,6 +92,18 @@ def main():
         if impl == "uccl" and registered and algo != "auto":
             tune.append({"coll": coll, "algo": algo, "proto": proto, "bytes": nbytes, "us": round(us, 3), "blocks": blocks})
 
+    def uccl_algo(coll, qname, algo, proto, dtn, nbytes, fn, it, busf):
+        """Time one (algorithm, protocol) at the tuner's CTA count and, from 256 KiB up, at every count of
+        --blocks; every result is recorded, the tuner table keeps the best per size."""
+        comm.set_algo(algo, proto)
+        comm.set_blocks(0)
+        record(coll, "uccl", algo, proto, dtn, nbytes, timed(fn, it), busf, True, comm.query_tuning(qname, nbytes, True)[2])
+        if nbytes >= (256 << 10) and algo in ("two_shot", "nvls") and proto == "simple":
+            for nb in env_blocks:
+                comm.set_blocks(nb)
+                record(coll, "uccl", algo, proto, dtn, nbytes, timed(fn, max(3, it // 2)), busf, True, nb)
+            comm.set_blocks(0)
+
     for dtn in args.dtypes.split(","):
         dt = dts[dtn]
         es = torch.empty((), dtype=dt).element_size()
@@ -114,9 +129,7 @@ def main():
                             continue
                         if algo == "copy_engine" and nbytes < (1 << 20):
                             continue
-                        comm.set_algo(algo, proto)
-                        record(coll, "uccl", algo, proto, dtn, nbytes, timed(lambda: comm.allreduce(sym), it), busf, True,
-                               comm.query_tuning("allreduce", nbytes, True)[2])
+                        uccl_algo(coll, "allreduce", algo, proto, dtn, nbytes, lambda: comm.allreduce(sym), it, busf)
                         if args.unregistered and algo in ("two_shot", "nvls", "one_shot"):
                             record(coll, "uccl", algo, proto, dtn, nbytes, timed(lambda: comm.allreduce(plain), it), busf, False)
                     comm.set_algo("auto", "auto")
@@ -133,8 +146,7 @@ def main():
                         for algo in (["nvls"] if nvls else []) + ["two_shot", "ring", "copy_engine"]:
                             if algo == "copy_engine" and nbytes < (1 << 20):
                                 continue
-                            comm.set_algo(algo, "simple")
-                            record(coll, "uccl", algo, "simple", dtn, nbytes, timed(lambda: comm.allgather(small, big_sym), it), busf, True)
+                            uccl_algo(coll, "allgather", algo, "simple", dtn, nbytes, lambda: comm.allgather(small, big_sym), it, busf)
                         if args.unregistered:
                             comm.set_algo("auto", "auto")
                             record(coll, "uccl", "auto", "auto", dtn, nbytes, timed(lambda: comm.allgather(small, big), it), busf, False)
@@ -143,12 +155,15 @@ def main():
                         for algo in (["nvls"] if nvls else []) + ["two_shot", "ring", "copy_engine"]:
                             if algo == "copy_engine" and nbytes < (1 << 20):
                                 continue
-                            comm.set_algo(algo, "simple")
-                            record(coll, "uccl", algo, "simple", dtn, nbytes, timed(lambda: comm.reduce_scatter(big_sym, small), it), busf, True)
+                            uccl_algo(coll, "reducescatter", algo, "simple", dtn, nbytes, lambda: comm.reduce_scatter(big_sym, small), it, busf)
                         if args.unregistered:
                             comm.set_algo("auto", "auto")
                             record(coll, "uccl", "auto", "auto", dtn, nbytes, timed(lambda: comm.reduce_scatter(big, small), it), busf, False)
                     comm.set_algo("auto", "auto")
+                    if coll == "allgather":
+                        record(coll, "uccl", "auto", "auto", dtn, nbytes, timed(lambda: comm.allgather(small, big_sym), it), busf, True)
+                    else:
+                        record(coll, "uccl", "auto", "auto", dtn, nbytes, timed(lambda: comm.reduce_scatter(big_sym, small), it), busf, True)
                     comm.free(big_sym)
                 elif coll == "broadcast":
                     cnt = nbytes // es
@@ -156,9 +171,9 @@ def main():
                     plain = torch.ones(cnt, dtype=dt, device=dev)
                     record(coll, "nccl", "nccl", "-", dtn, nbytes, timed(lambda: dist.broadcast(plain, 0), it), 1.0, False)
                     for algo in (["nvls"] if nvls else []) + ["two_shot"]:
-                        comm.set_algo(algo, "simple")
-                        record(coll, "uccl", algo, "simple", dtn, nbytes, timed(lambda: comm.broadcast(sym, 0), it), 1.0, True)
+                        uccl_algo(coll, "broadcast", algo, "simple", dtn, nbytes, lambda: comm.broadcast(sym, 0), it, 1.0)
                     comm.set_algo("auto", "auto")
+                    record(coll, "uccl", "auto", "auto", dtn, nbytes, timed(lambda: comm.broadcast(sym, 0), it), 1.0, True)
                     comm.free(sym)
                 elif coll == "alltoall":
                     cnt = max(1, nbytes // es // n)
@@ -194,7 +209,9 @@ def main():
                     f.write(json.dumps(r) + "\n")
         if args.tune:
             with open(args.tune, "w") as f:
-                json.dump({"version": 1, "nranks": n, "gpu": torch.cuda.get_device_name(dev), "entries": tune}, f)
+                json.dump({"version": 1, "nranks": n, "gpu": torch.cuda.get_device_name(dev), "nvls": nvls,
+                           "note": "symmetric buffers, device-timed max over ranks, benchmarks/sweep.py --tune",
+                           "entries": tune}, f, indent=0)
     barrier()
     comm.destroy()
     dist.destroy_process_group()

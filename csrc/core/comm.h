@@ -79,6 +79,9 @@ struct Comm {
   // topology + tuning
   TopoSystem topo;
   Tuner tuner;
+  void* netScratch = nullptr;  // device work copy of the network ring (reduce-scatter, reduce)
+  size_t netScratchBytes = 0;
+  std::string tuneTable;  // path of the shipped table that was loaded at creation, if any
   ucclAlgo_t forcedAlgo = ucclAlgoAuto;
   ucclProto_t forcedProto = ucclProtoAuto;
   int fusedAgMode = 0, fusedCommCtas = 0, fusedCeChunks = 0;  // ucclCommSetFusedOptions (0 = default)

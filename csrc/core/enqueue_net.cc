@@ -1,11 +1,12 @@
 // Collectives of a GPU communicator whose ranks cannot reach each other over NVLink (several
 // hosts, UCCL_FORCE_NET=1, or no peer access): the data crosses the network plugin.
 //
-// All-reduce runs as a persistent ring kernel that talks to the proxy thread through mapped
-// FIFOs (kernels/net_ring.cu), the arrangement of the reference's net ring
-// (src/algorithms/ring.cc:170-279).  The other collectives and point-to-point batches, which
-// the reference does not offer over the network at all, are staged through pinned host memory
-// and handed to the host ring; they synchronise the stream.
+// All-reduce, all-gather, reduce-scatter, broadcast and reduce run as a persistent ring kernel
+// that talks to the proxy thread through mapped FIFOs (kernels/net_ring.cu), the arrangement of
+// the reference's net ring (src/algorithms/ring.cc:170-279), stream-ordered.  All-to-all and
+// point-to-point batches, which need connections beyond the ring neighbours and which the
+// reference does not offer over the network at all, are staged through pinned host memory and
+// handed to the host transfer loop; those two wait for the stream.
 #include <string.h>
 
 #include "../host/host_coll.h"
@@ -14,7 +15,9 @@
 
 namespace uccl {
 
-ucclResult_t launchNetRingAllReduce(Comm* c, const CollOp& op);  // net_ring launcher (enqueue_netring.cc)
+// the ring kernel and its launcher (enqueue_netring.cc)
+bool netRingHandles(const CollOp& op);
+ucclResult_t launchNetRing(Comm* c, const CollOp& op);
 
 namespace {
 
@@ -39,7 +42,7 @@ ucclResult_t cudaFail(Comm* c, const char* what) {
 ucclResult_t enqueueNetGpu(Comm* c, const CollOp& op) {
   const size_t es = dataTypeSize(op.dtype);
   const int n = c->nRanks;
-  if (op.kind == ucclCollAllReduce && getenv("UCCL_NET_STAGED") == nullptr) return launchNetRingAllReduce(c, op);
+  if (netRingHandles(op) && getenv("UCCL_NET_STAGED") == nullptr) return launchNetRing(c, op);
 
   size_t sendBytes = op.count * es, recvBytes = op.count * es;
   if (op.kind == ucclCollAllGather) recvBytes *= n;

@@ -151,6 +151,8 @@ extern "C" ucclResult_t ucclAllReduceResidualRMSNorm(const void* x, const void* 
     const char* dbg = getenv("UCCL_NORM_DEBUG");
     a.debug = dbg ? atoi(dbg) : 0;
   }
+  a.mcRows = 1;
+  if (const char* e = getenv("UCCL_NORM_MC_ROWS")) a.mcRows = atoi(e);
   commCount(c, ucclCollAllReduce, bytes, c->arena && c->arena->mc ? ucclAlgoNvls : ucclAlgoTwoShot);
   if (c->nRanks == 1) {
     a.dc.nranks = 1;
@@ -286,10 +288,18 @@ extern "C" ucclResult_t ucclAllGatherGemm(const void* xShard, void* xFull, const
   }
   commCount(c, ucclCollAllGather, static_cast<size_t>(M) * K * 2, ucclAlgoOneShot);
   f.a_spread = agMode == 3 ? 1 : 0;
-  // The kernel reads my rows from the shard; a copy engine puts them into xFull meanwhile.
-  if (!f.a_inplace && (r = sideCopyBegin(c, const_cast<char*>(myRows), xShard, shardBytes, s)) != ucclSuccess) return r;
+  // Forwarder warps store through the switch when xFull has a multicast alias: one store stream
+  // that the switch replicates, instead of nranks - 1 unicast copies.  Between two GPUs there is
+  // nothing to replicate and plain peer stores are faster.  UCCL_FUSED_AG_MC=0/1 overrides.
+  bool viaSwitch = f.a_spread && sf.seg->mc != nullptr && n > 2 && c->forcedAlgo != ucclAlgoTwoShot && c->forcedAlgo != ucclAlgoOneShot;
+  if (const char* e = getenv("UCCL_FUSED_AG_MC")) viaSwitch = f.a_spread && sf.seg->mc != nullptr && atoi(e) != 0;
+  if (viaSwitch) f.a_full_mc = sf.seg->mc + sf.off;
+  // The kernel reads my rows from the shard; they reach xFull through the switch with everybody
+  // else's copy, or else a copy engine puts them there meanwhile.
+  const bool sideCopy = !f.a_inplace && !viaSwitch;
+  if (sideCopy && (r = sideCopyBegin(c, const_cast<char*>(myRows), xShard, shardBytes, s)) != ucclSuccess) return r;
   if ((r = launchGemmBf16(g, &f, s)) != ucclSuccess) return r;
-  if (!f.a_inplace) return sideCopyEnd(c, s);
+  if (sideCopy) return sideCopyEnd(c, s);
   return ucclSuccess;
 }
 

@@ -1,3 +1,4 @@
+#include <dlfcn.h>
 // Communicator lifecycle.  Follows the order of the reference's ucclCommInitRank
 // (src/init.cc:67-167: bootstrap -> plugin -> peer-info all-gather -> node count -> channels ->
 // proxy) and of its teardown (src/init.cc:210-240), but every resource the reference leaves as a
@@ -198,6 +199,44 @@ void buildChannels(Comm* c) {
   }
 }
 
+// The algorithm and CTA count per message size come from a table measured on this kind of machine
+// when one ships with the library: the directory "tuning" beside libuccl.so (or
+// ../share/uccl/tuning for an installed copy, or UCCL_TUNE_DIR) is searched for a table whose GPU
+// name, rank count and NVLS flag match this communicator.  UCCL_TUNE_FILE, when set, wins;
+// UCCL_TUNE_AUTO=0 keeps the built-in priors.  Replaces the fixed thresholds of the reference
+// (src/enqueue.cc:139-148, src/topo/topo_ring.cc:151-175).
+void autoLoadTuning(Comm* c) {
+  if (!c->cfg.tuneFile.empty() || c->backend != BACKEND_CUDA || !c->p2pReady || c->useNet || c->nRanks < 2) return;
+  if (const char* e = getenv("UCCL_TUNE_AUTO")) {
+    if (*e && atoi(e) == 0) return;
+  }
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, c->cudaDev) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return;
+  }
+  std::vector<std::string> dirs;
+  if (const char* e = getenv("UCCL_TUNE_DIR")) {
+    if (*e) dirs.push_back(e);
+  }
+  Dl_info info;
+  if (dladdr(reinterpret_cast<const void*>(&autoLoadTuning), &info) && info.dli_fname) {
+    std::string lib = info.dli_fname;
+    const size_t slash = lib.rfind('/');
+    const std::string dir = slash == std::string::npos ? "." : lib.substr(0, slash);
+    dirs.push_back(dir + "/tuning");
+    dirs.push_back(dir + "/../share/uccl/tuning");
+  }
+  for (const std::string& d : dirs) {
+    std::string chosen;
+    if (c->tuner.loadMatching(d, prop.name, c->nRanks, c->heap.nvls(), &chosen)) {
+      c->tuneTable = chosen;
+      UCCL_LOG(INFO, "tuning table %s", chosen.c_str());
+      return;
+    }
+  }
+}
+
 ucclResult_t initRank(Comm* c, const ucclUniqueId& id) {
   ucclResult_t r;
   c->cfg = loadConfig();
@@ -341,6 +380,7 @@ ucclResult_t initRank(Comm* c, const ucclUniqueId& id) {
     if ((r = netSetupRings(c)) != ucclSuccess) return r;
     if ((r = proxyStart(c)) != ucclSuccess) return r;
   }
+  autoLoadTuning(c);
   logSetRank(c->rank);
   UCCL_LOG(INFO, "communicator ready: rank %d/%d node %d/%d backend %s p2p %d nvls %d net %s channels %d", c->rank,
            c->nRanks, c->node, c->nNodes, c->backend == BACKEND_CUDA ? "cuda" : "cpu", (int)c->p2pReady,
@@ -369,6 +409,7 @@ void destroyComm(Comm* c) {
     if (c->onesDev) cudaFree(c->onesDev);
     if (c->rsSendBuf) cudaFree(c->rsSendBuf);
     if (c->rsCtl) cudaFree(c->rsCtl);
+    if (c->netScratch) cudaFree(c->netScratch);
     if (c->epochsDev) cudaFree(c->epochsDev);
     if (c->hostFlags) cudaFreeHost(c->hostFlags);
     traceDump(c);

@@ -55,6 +55,13 @@ class Tuner {
   void clear() { curves_.clear(); tableRanks_ = 0; }
   bool loadFile(const std::string& path, std::string* why);
   bool loadText(const std::string& json, std::string* why);
+  // Looks through the *.json tables of `dir` for one measured on this kind of machine: its "gpu"
+  // names the device (either string contains the other), "nranks" equals `nranks` and, if the
+  // table says so, "nvls" equals `nvls`.  Loads the first match (names in sorted order) and
+  // reports its path; false when there is none.
+  bool loadMatching(const std::string& dir, const std::string& gpuName, int nranks, bool nvls, std::string* chosen);
+  // The three header fields of a table, without loading it.
+  static bool tableHeader(const std::string& json, std::string* gpu, int* nranks, int* nvls);
   void addPoint(ucclCollKind_t coll, ucclAlgo_t algo, ucclProto_t proto, size_t bytes, float us, int blocks);
   TuneChoice choose(const TuneQuery& q) const;
   size_t numCurves() const { return curves_.size(); }

@@ -59,6 +59,50 @@ __device__ __forceinline__ uint4 reduce_peers(const CollArgs& a, size_t byteOff)
   return V::pack(acc);
 }
 
+// U vectors `stride` bytes apart from NP ranks each, all NP * U loads issued before the first add.
+// With two or four ranks a single vector per step leaves only two or four 16-byte loads in flight
+// per thread, far too few to cover the NVLink latency; callers pick U so that NP * U = 8.
+template <int DT, int U, int NP>
+__device__ __forceinline__ void reduce_peers_fixed(const CollArgs& a, size_t byteOff, size_t stride, uint4 (&out)[U]) {
+  using V = Vec<DT>;
+  uint4 v[U][NP];
+#pragma unroll
+  for (int j = 0; j < U; ++j)
+#pragma unroll
+    for (int p = 0; p < NP; ++p) v[j][p] = ptx::ld_stream_v4(a.in[(a.dc.rank + p) % NP] + byteOff + j * stride);
+#pragma unroll
+  for (int j = 0; j < U; ++j) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+    for (int p = 0; p < NP; ++p) V::add(acc, v[j][p]);
+    out[j] = V::pack(acc);
+  }
+}
+
+// out(i) for every 16-byte vector i in [begin, end) handled by this thread, with `sink(i, vector)`
+template <int DT, typename Sink>
+__device__ __forceinline__ void reduce_range(const CollArgs& a, size_t srcBase, size_t begin, size_t end, Sink sink) {
+  const size_t stride = static_cast<size_t>(blockDim.x) << 4;
+  const int n = a.dc.nranks;
+  size_t i = begin + (static_cast<size_t>(threadIdx.x) << 4);
+  if (n == 2) {
+    for (; i + 3 * stride < end; i += 4 * stride) {
+      uint4 o[4];
+      reduce_peers_fixed<DT, 4, 2>(a, srcBase + i, stride, o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) sink(i + j * stride, o[j]);
+    }
+  } else if (n == 4) {
+    for (; i + stride < end; i += 2 * stride) {
+      uint4 o[2];
+      reduce_peers_fixed<DT, 2, 4>(a, srcBase + i, stride, o);
+#pragma unroll
+      for (int j = 0; j < 2; ++j) sink(i + j * stride, o[j]);
+    }
+  }
+  for (; i < end; i += stride) sink(i, reduce_peers<DT>(a, srcBase + i));
+}
+
 // ------------------------------------------------------------------ all-reduce, one-shot
 template <int DT>
 __device__ void ar_oneshot(const CollArgs& a) {
@@ -69,8 +113,7 @@ __device__ void ar_oneshot(const CollArgs& a) {
   if (a.inUser) copy_clamped(const_cast<char*>(a.in[dc.rank]), a.inUser, off, len, a.userBytes);
   if (!rank_barrier(dc)) return;
   char* dst = a.out[dc.rank];
-  for (size_t i = off + (static_cast<size_t>(threadIdx.x) << 4); i < off + len; i += static_cast<size_t>(blockDim.x) << 4)
-    st_out16(dst + i, reduce_peers<DT>(a, i));
+  reduce_range<DT>(a, 0, off, off + len, [&](size_t i, uint4 v) { st_out16(dst + i, v); });
   if (!rank_barrier(dc)) return;
   if (a.outUser) copy_clamped(a.outUser, dst, off, len, a.userBytes);
 }
@@ -114,10 +157,9 @@ __device__ void ar_twoshot(const CollArgs& a) {
       }
       for (; i < end; i += stride) ptx::multimem_st_v4(a.outMc + i, V::mc_reduce(a.inMc + i));
     } else {
-      for (size_t i = begin + (static_cast<size_t>(threadIdx.x) << 4); i < end; i += stride) {
-        const uint4 v = reduce_peers<DT>(a, i);
+      reduce_range<DT>(a, 0, begin, end, [&](size_t i, uint4 v) {
         for (int p = 0; p < n; ++p) ptx::st_global_v4(a.out[(dc.rank + p) % n] + i, v);
-      }
+      });
     }
   }
   if (!rank_barrier(dc)) return;
@@ -283,6 +325,13 @@ __device__ void rs_pull(const CollArgs& a) {
   const size_t stride = static_cast<size_t>(blockDim.x) << 4;
   if (a.inMc) {
     size_t i = off + (static_cast<size_t>(threadIdx.x) << 4);
+    for (; i + 7 * stride < off + len; i += 8 * stride) {
+      uint4 v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = V::mc_reduce(a.inMc + src + i + j * stride);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) st_out16(dst + i + j * stride, v[j]);
+    }
     for (; i + 3 * stride < off + len; i += 4 * stride) {
       const uint4 v0 = V::mc_reduce(a.inMc + src + i), v1 = V::mc_reduce(a.inMc + src + i + stride);
       const uint4 v2 = V::mc_reduce(a.inMc + src + i + 2 * stride), v3 = V::mc_reduce(a.inMc + src + i + 3 * stride);
@@ -293,8 +342,7 @@ __device__ void rs_pull(const CollArgs& a) {
     }
     for (; i < off + len; i += stride) st_out16(dst + i, V::mc_reduce(a.inMc + src + i));
   } else {
-    for (size_t i = off + (static_cast<size_t>(threadIdx.x) << 4); i < off + len; i += stride)
-      st_out16(dst + i, reduce_peers<DT>(a, src + i));
+    reduce_range<DT>(a, src, off, off + len, [&](size_t i, uint4 v) { st_out16(dst + i, v); });
   }
   if (!rank_barrier(dc)) return;
   if (a.outUser) copy_clamped(a.outUser, dst, off, len, a.userBytes);
@@ -328,14 +376,23 @@ __device__ void bcast_push(const CollArgs& a) {
   if (!rank_barrier(dc)) return;
   if (dc.rank == a.root) {
     const size_t stride = static_cast<size_t>(blockDim.x) << 4;
-    for (size_t i = off + (static_cast<size_t>(threadIdx.x) << 4); i < off + len; i += stride) {
-      const uint4 v = ptx::ld_global_v4(a.inUser + i);
+    auto put = [&](size_t i, uint4 v) {
       if (a.outMc) {
         ptx::multimem_st_v4(a.outMc + i, v);
       } else {
         for (int p = 0; p < n; ++p) ptx::st_global_v4(a.out[(dc.rank + p) % n] + i, v);
       }
+    };
+    size_t i = off + (static_cast<size_t>(threadIdx.x) << 4);
+    for (; i + 3 * stride < off + len; i += 4 * stride) {  // four loads in flight per thread
+      const uint4 v0 = ptx::ld_global_v4(a.inUser + i), v1 = ptx::ld_global_v4(a.inUser + i + stride);
+      const uint4 v2 = ptx::ld_global_v4(a.inUser + i + 2 * stride), v3 = ptx::ld_global_v4(a.inUser + i + 3 * stride);
+      put(i, v0);
+      put(i + stride, v1);
+      put(i + 2 * stride, v2);
+      put(i + 3 * stride, v3);
     }
+    for (; i < off + len; i += stride) put(i, ptx::ld_global_v4(a.inUser + i));
   }
   rank_barrier(dc);
 }

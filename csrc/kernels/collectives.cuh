@@ -119,6 +119,7 @@ struct ArNormArgs {
   char* resOutUser;                      // set when `resOut` is the staging area: copy there last
   int tokens, hidden;
   float eps;
+  int mcRows;  // rows per pass of phase A on the switch path (1, 2 or 4)
   int debug;  // experiment switches (UCCL_NORM_DEBUG): 1 no phase B, 2 no phase-A stores, 4 no phase A
 };
 cudaError_t launchArNormKernel(const ArNormArgs& a, int blocks, cudaStream_t stream);

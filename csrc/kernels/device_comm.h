@@ -12,8 +12,8 @@ constexpr int kMaxBlocks = 128;       // CTAs a collective kernel may use ("chan
 constexpr int kLLBlocks = 16;         // CTAs the low-latency protocol may use
 constexpr int kLLDataPerBlock = 4096; // payload bytes per CTA per peer per LL operation
 constexpr int kLLSlotBytes = 2 * kLLDataPerBlock;  // each 8 data bytes travel with 8 flag bytes
-constexpr int kP2pSlots = 2;
-constexpr size_t kP2pSlotBytes = 2u << 20;
+constexpr int kP2pSlots = 4;               // FIFO depth per stripe: four pieces in flight hide the credit round trip
+constexpr size_t kP2pSlotBytes = 1u << 20;  // one slot of every stripe together (128 KiB per stripe)
 
 // Arena layout (byte offsets inside every rank's symmetric arena).
 constexpr size_t kArenaBarrierOff = 0;                 // u32 [kMaxBlocks][UCCL_MAX_LOCAL_RANKS]

@@ -145,7 +145,7 @@ __global__ void __launch_bounds__(kThreads, 1) ar_norm_kernel(const __grid_const
   // enough to cover the latency (the links, not the loads in flight, are the limit) and lets the
   // stores of one pass travel while the loads of the next are already out; the peer path takes R.
   const NormPass npB = np;
-  if (a.inMc) np.R = 1;
+  if (a.inMc) np.R = max(1, min(np.R, a.mcRows));
   for (size_t r0 = b; r0 < ((a.debug & 4) ? 0 : myLen); r0 += static_cast<size_t>(B) * np.R) {
     size_t rowIdx[kNormMaxRows];
     int rowsHere = 0;

@@ -215,6 +215,7 @@ ucclResult_t launchGemmBf16(const GemmLaunch& g, const GemmFusion* f, cudaStream
         c.ready_peer[i] = f->ready_peer[i];
       }
       c.a_shard = static_cast<const char*>(f->a_shard);
+      c.a_full_mc = static_cast<char*>(f->a_full_mc);
       c.a_inplace = f->a_inplace;
       a.a_ready = f->ready_peer[f->rank];
       // one count per copied piece of a row block (see comm_allgather_push / _push2d)

@@ -98,6 +98,7 @@ struct CommArgs {
   const char* a_shard = nullptr;
   int a_inplace = 0;
   char* a_full_peer[kMaxPeers] = {};
+  char* a_full_mc = nullptr;   // multicast alias of A_full (NVSwitch replicates one store to every rank) or nullptr
   uint32_t* ready_peer[kMaxPeers] = {};  // every rank's arrival counters, one per 128-row block, zero at launch
   // reduce-scatter: every rank owns a staging buffer [nranks][rows_per_rank][N]; slot s receives
   // rank s's partial result for the owner's rows (tensor maps in PeerMaps)
@@ -327,6 +328,62 @@ __device__ void comm_allgather_push(const Args& a, uint8_t* smem, uint64_t* bars
   }
   ptx::tma_store_wait<0>();
   for (int i = total > LAG ? total - LAG : 0; i < total; ++i) completed(i);
+  flush();
+}
+
+// ------------------------------------------------------------------ all-gather push through the switch
+// Forwarder warp of "spread" mode when A_full has a multicast alias: the 32 lanes read this CTA's
+// share of the shard with 16-byte loads and write it with multimem.st, which the switch
+// replicates into every rank's A_full (this rank's own copy included).  One store stream instead
+// of nranks - 1 unicast copies: the SM that also runs the GEMM issues a seventh of the stores at
+// eight ranks.  Pieces and counting are those of comm_allgather_push with FWD_SLOT_BYTES pieces:
+// one add per (row block, rank) covering this CTA's pieces of the block.
+__device__ void comm_allgather_push_mc(const Args& a, int cta, int nctas, int lane) {
+  const CommArgs& c = a.comm;
+  const int n = c.nranks, r = c.rank, bpr = a.m_bpr;
+  const size_t blkBytes = static_cast<size_t>(BM) * a.K * 2;
+  const int nsub = static_cast<int>((blkBytes + FWD_SLOT_BYTES - 1) / FWD_SLOT_BYTES);
+  const int allPieces = bpr * nsub;
+  const size_t shardOff = static_cast<size_t>(r) * bpr * blkBytes;
+  int curBlk = -1;
+  uint32_t cnt = 0;
+  auto flush = [&]() {
+    if (curBlk < 0 || cnt == 0) return;
+    // every lane orders its own stores, then lane 0 publishes the count
+    ptx::fence_sys();
+    __syncwarp();
+    if (lane == 0) {
+      for (int q = 1; q < n; ++q) {
+        const int p = (r + q) % n;
+        ptx::red_release_sys_add_u32(c.ready_peer[p] + static_cast<size_t>(r * bpr + curBlk) * FLAG_STRIDE, cnt);
+      }
+    }
+    cnt = 0;
+  };
+  for (int g = cta; g < allPieces; g += nctas) {
+    const int blk = g / nsub, sub = g - blk * nsub;
+    if (blk != curBlk) {
+      flush();
+      curBlk = blk;
+    }
+    const size_t off = static_cast<size_t>(blk) * blkBytes + static_cast<size_t>(sub) * FWD_SLOT_BYTES;
+    const size_t left = blkBytes - static_cast<size_t>(sub) * FWD_SLOT_BYTES;
+    const uint32_t bytes = static_cast<uint32_t>(left < FWD_SLOT_BYTES ? left : FWD_SLOT_BYTES);
+    const char* src = c.a_shard + off;
+    char* dst = c.a_full_mc + shardOff + off;
+    // blkBytes is a multiple of 16 (K % 8 == 0): whole vectors only; four loads in flight per lane
+    uint32_t i = static_cast<uint32_t>(lane) << 4;
+    for (; i + 3 * 512 < bytes; i += 4 * 512) {
+      const uint4 v0 = ptx::ld_global_v4(src + i), v1 = ptx::ld_global_v4(src + i + 512);
+      const uint4 v2 = ptx::ld_global_v4(src + i + 1024), v3 = ptx::ld_global_v4(src + i + 1536);
+      ptx::multimem_st_v4(dst + i, v0);
+      ptx::multimem_st_v4(dst + i + 512, v1);
+      ptx::multimem_st_v4(dst + i + 1024, v2);
+      ptx::multimem_st_v4(dst + i + 1536, v3);
+    }
+    for (; i < bytes; i += 512) ptx::multimem_st_v4(dst + i, ptx::ld_global_v4(src + i));
+    ++cnt;
+  }
   flush();
 }
 
@@ -853,8 +910,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   } else if (warp == 6) {
     // ------------------------------------------------------------ forwarder (all-gather, spread mode)
-    if (COMM == kCommAllGather && a.a_spread && lane == 0 && !(a.debug & 1))
-      comm_allgather_push<FWD_SLOT_BYTES, FWD_SLOTS, 2, 2>(a, smem + PIPE_BYTES, bars + 24, blockIdx.x, gridDim.x);
+    if (COMM == kCommAllGather && a.a_spread && !(a.debug & 1)) {
+      if (a.comm.a_full_mc) comm_allgather_push_mc(a, blockIdx.x, gridDim.x, lane);
+      else if (lane == 0) comm_allgather_push<FWD_SLOT_BYTES, FWD_SLOTS, 2, 2>(a, smem + PIPE_BYTES, bars + 24, blockIdx.x, gridDim.x);
+    }
   } else {
     // ------------------------------------------------------------ epilogue warps
     const int q = warp & 3;  // TMEM lane quarter this warp may access
@@ -1041,8 +1100,10 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
   } else if (warp == 6) {
     // ------------------------------------------------------------ forwarder (all-gather, spread mode)
-    if (COMM == kCommAllGather && a.a_spread && lane == 0 && !(a.debug & 1))
-      comm_allgather_push<FWD_SLOT_BYTES, FWD_SLOTS, 2, 2>(a, smem + PIPE_BYTES, bars + 24, blockIdx.x, gridDim.x);
+    if (COMM == kCommAllGather && a.a_spread && !(a.debug & 1)) {
+      if (a.comm.a_full_mc) comm_allgather_push_mc(a, blockIdx.x, gridDim.x, lane);
+      else if (lane == 0) comm_allgather_push<FWD_SLOT_BYTES, FWD_SLOTS, 2, 2>(a, smem + PIPE_BYTES, bars + 24, blockIdx.x, gridDim.x);
+    }
   } else {
     // ------------------------------------------------------------ epilogue warps (both CTAs)
     const int q = warp & 3;

@@ -36,6 +36,7 @@ struct GemmFusion {
   int a_peer_major = 0;  // visit the other ranks' shards one rank after the other, nearest first (copy-engine lanes)
   int a_spread = 0;    // no communication CTAs either: a forwarder warp in every GEMM CTA pushes the shard
   void* a_full_peer[UCCL_MAX_LOCAL_RANKS] = {};
+  void* a_full_mc = nullptr;  // multicast alias of A_full: the forwarder warps store through the switch
   uint32_t* ready_peer[UCCL_MAX_LOCAL_RANKS] = {};
   // reduce-scatter: every rank's staging buffer [nranks][rows_per_rank][N] (peer-mapped) and
   // per-row-block counters (zeroed before the launch); output of this rank

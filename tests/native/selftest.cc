@@ -7,6 +7,7 @@
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
+#include <unistd.h>
 
 #include <cmath>
 #include <deque>
@@ -370,6 +371,39 @@ std::string testTuner() {
   EXPECT(!t.loadText("{\"entries\":[]}", &why));
   EXPECT(!t.loadText("not json", &why));
   EXPECT(t.numCurves() == 3);  // a rejected table leaves the old one in place
+  // shipped tables are matched by GPU name, rank count and NVLS flag
+  {
+    char dir[] = "/tmp/uccl_tune_XXXXXX";
+    EXPECT(mkdtemp(dir) != nullptr);
+    auto put = [&](const char* name, const char* gpu, int ranks, const char* nvls, double us) {
+      const std::string path = std::string(dir) + "/" + name;
+      FILE* f = fopen(path.c_str(), "w");
+      if (!f) return;
+      fprintf(f, "{\"version\":1,\"gpu\":\"%s\",\"nranks\":%d%s,\"entries\":[{\"coll\":\"allreduce\",\"algo\":\"two_shot\","
+                 "\"proto\":\"simple\",\"bytes\":4096,\"us\":%f,\"blocks\":3}]}", gpu, ranks, nvls, us);
+      fclose(f);
+    };
+    put("a_other_gpu.json", "NVIDIA H100", 8, "", 1.0);
+    put("b_b200_x4.json", "NVIDIA B200", 4, "", 2.0);
+    put("c_b200_x8_nonvls.json", "NVIDIA B200", 8, ",\"nvls\":false", 3.0);
+    put("d_b200_x8.json", "NVIDIA B200", 8, ",\"nvls\":true", 4.0);
+    put("e_not_a_table.json", "NVIDIA B200", 8, "", -1.0);
+    Tuner m;
+    std::string chosen;
+    EXPECT(m.loadMatching(dir, "NVIDIA B200", 8, true, &chosen));
+    EXPECT(chosen.find("d_b200_x8.json") != std::string::npos && m.tableRanks() == 8);
+    EXPECT(m.loadMatching(dir, "NVIDIA B200", 8, false, &chosen) && chosen.find("c_b200_x8_nonvls") != std::string::npos);
+    EXPECT(m.loadMatching(dir, "NVIDIA B200", 4, true, &chosen) && chosen.find("b_b200_x4") != std::string::npos);
+    EXPECT(!m.loadMatching(dir, "NVIDIA B200", 2, true, &chosen));
+    EXPECT(!m.loadMatching(dir, "NVIDIA A100", 8, true, &chosen));
+    EXPECT(!m.loadMatching(std::string(dir) + "/missing", "NVIDIA B200", 8, true, &chosen));
+    std::string gpu;
+    int ranks = 0, nv = 0;
+    EXPECT(Tuner::tableHeader("{\"gpu\":\"X\",\"nranks\":2}", &gpu, &ranks, &nv) && gpu == "X" && ranks == 2 && nv == -1);
+    for (const char* n : {"a_other_gpu.json", "b_b200_x4.json", "c_b200_x8_nonvls.json", "d_b200_x8.json", "e_not_a_table.json"})
+      unlink((std::string(dir) + "/" + n).c_str());
+    rmdir(dir);
+  }
   // reductions on a type that cannot be summed are never offered
   q.reducible = false;
   EXPECT(!Tuner::feasible(q, ucclAlgoTwoShot, ucclProtoSimple));

@@ -441,8 +441,7 @@ def case_tp_mlp(comm, rank, n, args):
     fail = []
     # every way of moving the all-gather's rows: copy engines, dedicated CTAs, a forwarder warp per CTA
     modes = [("ce", "kernel"), ("kernel", "kernel"), ("spread", "kernel")] if n > 1 else [("ce", "kernel")]
-    # the copy-engine reduce-scatter is opt-in until it has been run on GPUs
-    if n > 1 and os.environ.get("UCCL_TEST_FUSED_RS_CE"):
+    if n > 1:  # reduce-scatter carried by copy engines
         modes += [("spread", "ce"), ("ce", "ce")]
     for ag_mode, rs_mode in modes:
         os.environ["UCCL_FUSED_AG"] = ag_mode
