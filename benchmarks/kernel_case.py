@@ -5,6 +5,7 @@
     python benchmarks/kernel_case.py --case gemm_swiglu --m 4096 --n 7168 --k 4096
     python benchmarks/kernel_case.py --case add_norm --tokens 8192 --hidden 8192
     python benchmarks/kernel_case.py --case moe_dispatch --tokens 4096 --hidden 7168
+    python benchmarks/kernel_case.py --case moe_combine --tokens 4096 --hidden 7168
     python benchmarks/kernel_case.py --case gemm_rs_self --m 8192 --n 4096 --k 1792
 
 Prints one JSON line with the median device time and the achieved fraction of the measured
@@ -86,6 +87,24 @@ def main():
         idx = torch.randn(args.tokens, args.experts, device=dev).topk(args.topk, dim=-1).indices.to(torch.int32).contiguous()
         t = device_time_ms(lambda: disp.dispatch(x, idx), args.iters, args.warmup)
         nbytes = x.numel() * 2 + args.tokens * args.topk * (args.hidden + args.hidden // 32 + 16)
+        out.update(tokens=args.tokens, hidden=args.hidden, topk=args.topk, ms=round(t["median"], 4),
+                   gbs=round(nbytes / t["median"] / 1e6, 1), frac_of_copy_bw=round(nbytes / t["median"] / 1e6 / peaks["hbm_gbs"], 3))
+        disp.close()
+        comm.destroy()
+    elif args.case == "moe_combine":
+        from unified_ccl_b200 import Communicator
+        from unified_ccl_b200.parallel import MoeDispatcher
+
+        comm = Communicator(0, 1)
+        disp = MoeDispatcher(comm, args.tokens, args.hidden, args.experts, args.topk)
+        x = torch.randn(args.tokens, args.hidden, device=dev).to(torch.bfloat16)
+        w, idx = torch.softmax(torch.randn(args.tokens, args.experts, device=dev), -1).topk(args.topk, dim=-1)
+        disp.dispatch(x, idx.to(torch.int32).contiguous())
+        disp.expert_out.normal_()
+        y = torch.empty(args.tokens, args.hidden, device=dev, dtype=torch.bfloat16)
+        wf = w.float().contiguous()
+        t = device_time_ms(lambda: disp.combine(wf, out=y), args.iters, args.warmup)
+        nbytes = args.tokens * args.topk * args.hidden * 2 + y.numel() * 2
         out.update(tokens=args.tokens, hidden=args.hidden, topk=args.topk, ms=round(t["median"], 4),
                    gbs=round(nbytes / t["median"] / 1e6, 1), frac_of_copy_bw=round(nbytes / t["median"] / 1e6 / peaks["hbm_gbs"], 3))
         disp.close()

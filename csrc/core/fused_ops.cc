@@ -105,6 +105,13 @@ bool fusedSelf() {
   return s && atoi(s) != 0;
 }
 
+// UCCL_FUSED_FOLD_BARRIER=0 runs the rank barrier of a fused launch as a kernel of its own in
+// front of it (the older arrangement) instead of inside the GEMM kernel's prologue.
+bool foldBarrier() {
+  const char* s = getenv("UCCL_FUSED_FOLD_BARRIER");
+  return !(s && *s && atoi(s) == 0);
+}
+
 struct Sym {
   SymSegment* seg = nullptr;
   size_t off = 0;
@@ -147,10 +154,12 @@ extern "C" ucclResult_t ucclAllReduceResidualRMSNorm(const void* x, const void* 
   a.tokens = tokens;
   a.hidden = hidden;
   a.eps = eps;
+#ifdef UCCL_EXPERIMENTS
   {
     const char* dbg = getenv("UCCL_NORM_DEBUG");
     a.debug = dbg ? atoi(dbg) : 0;
   }
+#endif
   a.mcRows = 1;
   if (const char* e = getenv("UCCL_NORM_MC_ROWS")) a.mcRows = atoi(e);
   commCount(c, ucclCollAllReduce, bytes, c->arena && c->arena->mc ? ucclAlgoNvls : ucclAlgoTwoShot);
@@ -233,7 +242,7 @@ extern "C" ucclResult_t ucclAllGatherGemm(const void* xShard, void* xFull, const
     commSetError(c, "all-gather GEMM needs M / nranks to be a multiple of 128 (M=%d, nranks=%d)", M, n);
     return ucclInvalidArgument;
   }
-  if (M / 128 > kGemmMaxRowBlocks) return ucclInvalidArgument;
+  if (M / 128 >= kGemmMaxRowBlocks) return ucclInvalidArgument;  // one more line holds the launch's go flag
   Sym sf;
   if (!symOf(c, xFull, static_cast<size_t>(M) * K * 2, &sf)) {
     commSetError(c, "xFull must come from ucclMemAlloc");
@@ -245,10 +254,18 @@ extern "C" ucclResult_t ucclAllGatherGemm(const void* xShard, void* xFull, const
   if (reinterpret_cast<uintptr_t>(xShard) & 15) return ucclInvalidArgument;
   // Arrival counters start at zero.  The barrier orders the zeroing before any rank's pushes, and
   // those pushes after every rank's previous readers of its xFull.
+  // With copy engines the pushes start from the host side, so the barrier stays a kernel of its own;
+  // otherwise it runs inside the GEMM launch (the word after the last counter is its `go` flag).
   uint32_t* ready = reinterpret_cast<uint32_t*>(c->arena->local + kArenaGemmReadyOff);
-  if (cudaMemsetAsync(ready, 0, kGemmFlagStrideBytes * (M / 128), s) != cudaSuccess) return ucclSystemError;
-  if ((r = enqueueBarrier(c, s)) != ucclSuccess) return r;
+  if (cudaMemsetAsync(ready, 0, kGemmFlagStrideBytes * (M / 128 + 1), s) != cudaSuccess) return ucclSystemError;
+  const bool fold = foldBarrier() && fusedAgMode(c) != 1;
+  if (!fold && (r = enqueueBarrier(c, s)) != ucclSuccess) return r;
   GemmFusion f;
+  if (fold) {
+    f.arena_peer = c->dev.arena;
+    f.epochs = c->dev.epochs;
+    f.go = ready + static_cast<size_t>(M / 128) * (kGemmFlagStrideBytes / 4);
+  }
   f.role = 1;
   f.rank = c->localRank;
   f.nranks = n;
@@ -331,7 +348,7 @@ extern "C" ucclResult_t ucclGemmReduceScatter(const void* A, const void* W, void
     commSetError(c, "GEMM reduce-scatter needs M / nranks to be a multiple of 128 and N a multiple of 8");
     return ucclInvalidArgument;
   }
-  if (M / 128 > kGemmMaxRowBlocks) return ucclInvalidArgument;
+  if (M / 128 >= kGemmMaxRowBlocks) return ucclInvalidArgument;  // one more line holds the launch's go flag
   Sym sp;
   if (!symOf(c, cPartial, static_cast<size_t>(M) * N * 2, &sp)) {
     commSetError(c, "cPartial must come from ucclMemAlloc");
@@ -341,7 +358,9 @@ extern "C" ucclResult_t ucclGemmReduceScatter(const void* A, const void* W, void
   // partial sums of this rank's rows.  The counters start at zero, and the barrier also orders
   // this launch's remote writes after every rank's previous use of its staging buffer.
   uint32_t* done = reinterpret_cast<uint32_t*>(c->arena->local + kArenaGemmDoneOff);
-  if (cudaMemsetAsync(done, 0, kGemmFlagStrideBytes * (M / 128), s) != cudaSuccess) return ucclSystemError;
+  if (cudaMemsetAsync(done, 0, kGemmFlagStrideBytes * (M / 128 + 1), s) != cudaSuccess) return ucclSystemError;
+  const bool fold = foldBarrier();
+  uint32_t* go = done + static_cast<size_t>(M / 128) * (kGemmFlagStrideBytes / 4);
   const int rsChunks = fusedRsCeChunks(c, M / n / 128);
   if (rsChunks > 0) {
     // ---- copy engines carry the slabs (see reduceScatterPushCopies)
@@ -373,8 +392,13 @@ extern "C" ucclResult_t ucclGemmReduceScatter(const void* A, const void* W, void
     if (cudaMemsetAsync(c->rsCtl, 0, 4096, s) != cudaSuccess ||
         cudaMemsetAsync(ceDone, 0, kGemmFlagStrideBytes * n * rsChunks, s) != cudaSuccess)
       return ucclSystemError;
-    if ((r = enqueueBarrier(c, s)) != ucclSuccess) return r;
+    if (!fold && (r = enqueueBarrier(c, s)) != ucclSuccess) return r;
     GemmFusion f;
+    if (fold) {
+      f.arena_peer = c->dev.arena;
+      f.epochs = c->dev.epochs;
+      f.go = go;
+    }
     f.role = 3;
     f.rank = c->localRank;
     f.nranks = n;
@@ -408,8 +432,13 @@ extern "C" ucclResult_t ucclGemmReduceScatter(const void* A, const void* W, void
     }
     return reduceScatterPushEnd(c, slabFlag, (n - 1) * rsChunks, s);
   }
-  if ((r = enqueueBarrier(c, s)) != ucclSuccess) return r;
+  if (!fold && (r = enqueueBarrier(c, s)) != ucclSuccess) return r;
   GemmFusion f;
+  if (fold) {
+    f.arena_peer = c->dev.arena;
+    f.epochs = c->dev.epochs;
+    f.go = go;
+  }
   f.role = 2;
   f.rank = c->localRank;
   f.nranks = n;

@@ -9,6 +9,7 @@
 
 #include "../core/cuda_driver.h"
 #include "../core/log.h"
+#include "device_comm.h"
 #include "gemm_sm100.cuh"
 
 namespace uccl {
@@ -183,13 +184,19 @@ ucclResult_t launchGemmBf16(const GemmLaunch& g, const GemmFusion* f, cudaStream
     a.tiles_n = (g.N + gemm::BN - 1) / gemm::BN;
   }
   a.err = g.err;
+#ifdef UCCL_EXPERIMENTS
   {
     const char* dbg = getenv("UCCL_FUSED_DEBUG");
     a.debug = dbg ? atoi(dbg) : 0;
   }
+#endif
   // UCCL_GEMM_TIMES=1: CTA 0 stamps the phases of every launch; the launcher waits and prints them
   static unsigned long long* timesDev = nullptr;
+#ifdef UCCL_EXPERIMENTS
   const bool wantTimes = getenv("UCCL_GEMM_TIMES") != nullptr;
+#else
+  const bool wantTimes = false;
+#endif
   if (wantTimes) {
     if (!timesDev) cudaMalloc(&timesDev, 48 * sizeof(unsigned long long));
     cudaMemsetAsync(timesDev, 0, 48 * sizeof(unsigned long long), stream);
@@ -206,6 +213,14 @@ ucclResult_t launchGemmBf16(const GemmLaunch& g, const GemmFusion* f, cudaStream
     c.timeout_ns = f->timeout_ns;
     c.abort_flag = f->abort_flag;
     c.rows_per_rank = f->rows_per_rank;
+    if (f->go && f->arena_peer && f->epochs) {
+      // the fused kernels' own barrier slot: the last CTA index a collective may use
+      constexpr int kSlot = kMaxBlocks - 1;
+      for (int i = 0; i < f->nranks; ++i)
+        c.bar_row_peer[i] = reinterpret_cast<uint32_t*>(f->arena_peer[i] + kArenaBarrierOff) + kSlot * UCCL_MAX_LOCAL_RANKS;
+      c.bar_epoch = f->epochs + kSlot;
+      c.go = f->go;
+    }
     const int blk_per_rank = f->rows_per_rank / gemm::BM;
     a.m_bpr = blk_per_rank;
     if (role == gemm::kCommAllGather) {
@@ -231,7 +246,7 @@ ucclResult_t launchGemmBf16(const GemmLaunch& g, const GemmFusion* f, cudaStream
         a.a_own_shard = 1;
         if (!makeTensorMap(&pm.m[0], f->a_shard, f->rows_per_rank, g.K, g.K, gemm::BK, gemm::BM)) return ucclSystemError;
       }
-      a.m_order = (a.debug & 4) ? 0 : (f->a_peer_major ? 3 : 1);
+      a.m_order = (a.debug & 4) ? 0 : (f->a_peer_major ? 3 : 1);  // debug is zero outside experiment builds
     } else if (role == gemm::kCommReduceScatterCe) {
       // copy engines carry the slabs: the kernel only writes local memory and counts
       if (!usePairKernel() || f->rows_per_rank % (2 * gemm::BM) != 0 || f->ce_chunks < 1 ||

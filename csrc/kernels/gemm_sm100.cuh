@@ -37,6 +37,16 @@
 #include <cuda.h>
 #include "ptx.cuh"
 
+// Phase-skipping switches (Args.debug) and in-kernel time stamps (Args.times) exist only in builds
+// made with UCCL_EXPERIMENTS=1 (benchmarks/tp_breakdown.py); product builds compile them out.
+#ifdef UCCL_EXPERIMENTS
+#define UCCL_DBG(a, bit) (((a).debug & (bit)) != 0)
+#define UCCL_TIMES(a) ((a).times)
+#else
+#define UCCL_DBG(a, bit) false
+#define UCCL_TIMES(a) static_cast<unsigned long long*>(nullptr)
+#endif
+
 namespace uccl {
 namespace gemm {
 
@@ -92,6 +102,11 @@ struct CommArgs {
   int nranks = 1;
   uint64_t timeout_ns = 0;         // deadline for cross-rank waits
   uint32_t* abort_flag = nullptr;  // comm-wide abort word (device-visible)
+  // rank barrier folded into the launch: GEMM CTA 0 meets CTA 0 of every rank, then raises `go`;
+  // nothing is written to a peer and no flag is raised for a copy engine before that
+  uint32_t* bar_row_peer[kMaxPeers] = {};  // every rank's barrier words of the fused kernels' slot, indexed by source rank
+  uint32_t* bar_epoch = nullptr;            // local: barriers done so far on that slot
+  uint32_t* go = nullptr;                   // local, zero at launch: 1 = every rank has arrived, 2 = gave up; nullptr = no folded barrier
   int rows_per_rank = 0;           // multiple of 128
   // all-gather: A_full is a symmetric [M, K] buffer; my shard is pushed into rows
   // [rank * rows_per_rank, ...) of every rank's copy (my own included unless it is already there)
@@ -176,6 +191,53 @@ __device__ __forceinline__ bool wait_flag_geq(const uint32_t* flag, uint32_t tar
   }
 }
 
+// The launch's rank barrier, run by lanes 1 .. nranks of one otherwise idle warp of GEMM CTA 0
+// (lane p + 1 deals with rank p) while the GEMM roles already work on tiles that need no peer:
+// same words and epochs as the collectives' CTA barrier (coll_device.cuh rank_barrier), on a slot
+// of its own.  Raises `go` for everybody who is about to touch a peer.
+__device__ __forceinline__ void prologue_barrier(const CommArgs& c, int lane, uint32_t* err) {
+  if (lane < 1 || lane > c.nranks) return;
+  const unsigned mask = ((c.nranks >= 31 ? 0xffffffffu : ((1u << (c.nranks + 1)) - 1u))) & ~1u;
+  const int p = lane - 1;
+  const uint32_t e = *c.bar_epoch + 1;
+  ptx::fence_sys();
+  ptx::st_release_sys_u32(c.bar_row_peer[p] + c.rank, e);
+  const uint32_t* mine = c.bar_row_peer[c.rank] + p;
+  bool ok = true;
+  const uint64_t t0 = ptx::globaltimer_ns();
+  const uint64_t limit = c.timeout_ns ? c.timeout_ns : 10000000000ull;
+  uint32_t spins = 0;
+  while (static_cast<int32_t>(ptx::ld_relaxed_sys_u32(mine) - e) < 0) {
+    if ((++spins & 31u) == 0) {
+      if ((c.abort_flag && ptx::ld_relaxed_sys_u32(c.abort_flag)) || ptx::globaltimer_ns() - t0 > limit) {
+        ok = false;
+        break;
+      }
+    }
+  }
+  ptx::fence_sys();
+  const bool all = __all_sync(mask, ok);
+  if (lane == 1) {
+    *c.bar_epoch = e;  // advance even on failure: the peers did too
+    if (!all && err) atomicCAS(err, 0u, 0x42415252u);
+    __threadfence();
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(c.go), "r"(all ? 1u : 2u) : "memory");
+  }
+}
+// Wait for the folded barrier (one thread).  True when every rank has arrived.
+__device__ __forceinline__ bool wait_go(const CommArgs& c) {
+  if (!c.go) return true;
+  const uint64_t t0 = ptx::globaltimer_ns();
+  const uint64_t limit = (c.timeout_ns ? c.timeout_ns : 10000000000ull) + 1000000000ull;
+  uint32_t spins = 0, v;
+  while (true) {
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(c.go) : "memory");
+    if (v != 0) return v == 1;
+    if ((++spins & 63u) == 0 && ptx::globaltimer_ns() - t0 > limit) return false;
+    __nanosleep(64);
+  }
+}
+
 // logical row-block index (in units of `unit` 128-row blocks per tile row) -> physical
 __device__ __forceinline__ int order_rows(const Args& a, int m, int tiles_rows, int unit) {
   if (a.m_order == 1) {
@@ -249,7 +311,11 @@ __device__ void comm_allgather_push(const Args& a, uint8_t* smem, uint64_t* bars
   for (int s = 0; s < SLOTS; ++s) ptx::mbar_init(&full[s], 1);
   ptx::mbar_fence_init();
   volatile uint32_t bail = 0;
+#ifdef UCCL_EXPERIMENTS
   const int mapMode = (a.debug >> 10) & 3;  // experiments: 1 whole blocks per CTA, 2 one contiguous range per CTA
+#else
+  constexpr int mapMode = 0;
+#endif
   int total = 0;
   if (mapMode == 0) {
     for (int g = cta; g < allPieces; g += nctas) ++total;
@@ -634,14 +700,14 @@ __device__ void reduce_scatter_tail(const Args& a, uint8_t* smem, uint64_t* tbar
   const bool contig = static_cast<size_t>(c.rs_ldo) * 2 == rowBytes;
   const size_t outRowBytes = static_cast<size_t>(c.rs_ldo) * 2;
   const int warp = threadIdx.x >> 5;
-  if (a.times && cta == 0 && threadIdx.x == 0) a.times[2] = ptx::globaltimer_ns();
+  if (UCCL_TIMES(a) && cta == 0 && threadIdx.x == 0) a.times[2] = ptx::globaltimer_ns();
   for (int i = 0; i < myUnits; ++i) {
     // stage (i + 2) % 3 was consumed in iteration i - 1, which ended with a CTA barrier
     if (threadIdx.x == 0 && i + TSTAGES - 1 < myUnits && !*bail) issue(i + TSTAGES - 1);
     const int st = i % TSTAGES;
     bool ok = true;
     if (warp != 0) ok = ptx::mbar_wait_bounded(&tbars[st], (i / TSTAGES) & 1, bail);
-    if (a.times && cta == 0 && threadIdx.x == 32 && i < 8) a.times[16 + 2 * i] = ptx::globaltimer_ns();
+    if (UCCL_TIMES(a) && cta == 0 && threadIdx.x == 32 && i < 8) a.times[16 + 2 * i] = ptx::globaltimer_ns();
     if (warp != 0 && ok) {
       const int u = cta + i * nctas;
       const int b = u / pieces, part = u - b * pieces;
@@ -656,10 +722,10 @@ __device__ void reduce_scatter_tail(const Args& a, uint8_t* smem, uint64_t* tbar
       else if (n == 4) tail_sum_piece<4>(sbase, P, n, nv, dst, contig, c.rs_out, row0, colb0, rb, outRowBytes, t, nt);
       else if (n == 8) tail_sum_piece<8>(sbase, P, n, nv, dst, contig, c.rs_out, row0, colb0, rb, outRowBytes, t, nt);
       else tail_sum_piece<0>(sbase, P, n, nv, dst, contig, c.rs_out, row0, colb0, rb, outRowBytes, t, nt);
-      if (a.times && cta == 0 && threadIdx.x == 32 && i < 8) a.times[17 + 2 * i] = ptx::globaltimer_ns();
+      if (UCCL_TIMES(a) && cta == 0 && threadIdx.x == 32 && i < 8) a.times[17 + 2 * i] = ptx::globaltimer_ns();
     }
     if (__syncthreads_or(ok ? 0 : 1)) break;
-    if (a.times && cta == 0 && threadIdx.x == 0 && i < 12) a.times[3 + i] = ptx::globaltimer_ns();
+    if (UCCL_TIMES(a) && cta == 0 && threadIdx.x == 0 && i < 12) a.times[3 + i] = ptx::globaltimer_ns();
   }
 }
 
@@ -674,7 +740,7 @@ __device__ __forceinline__ void epilogue_tile(const Args& a, const PeerMaps& pm,
     const int rpr = a.comm.rows_per_rank;
     const int owner = min((mb * BM) / rpr, a.comm.nranks - 1);
     const int drow = a.comm.rank * rpr + (mb * BM + q * 32 - owner * rpr);
-    const CUtensorMap* dmap = &pm.m[(a.debug & 16) ? a.comm.rank : owner];
+    const CUtensorMap* dmap = &pm.m[UCCL_DBG(a, 16) ? a.comm.rank : owner];
 #pragma unroll 1
     for (int g = 0; g < BN / 64; ++g) {
       uint32_t r0[32], r1[32];
@@ -699,7 +765,7 @@ __device__ __forceinline__ void epilogue_tile(const Args& a, const PeerMaps& pm,
       const int col0 = nb * BN + g * 64;
       ptx::fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0 && col0 < a.N && !(a.debug & 2)) {
+      if (lane == 0 && col0 < a.N && !UCCL_DBG(a, 2)) {
         ptx::tma_store_2d(dmap, buf, col0, drow);
       }
       if (lane == 0) ptx::tma_store_commit();  // exactly BN / 64 groups per tile
@@ -793,7 +859,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PIPE_BYTES + EPI_STAGE_BYTES);
   if (COMM == kCommAllGather && static_cast<int>(blockIdx.x) < a.comm_ctas) {
-    if (!(a.debug & 1) && threadIdx.x == 0)
+    if (!UCCL_DBG(a, 1) && threadIdx.x == 0 && wait_go(a.comm))
       comm_allgather_push<COPY_SLOT_BYTES, COPY_SLOTS, 4, 4>(a, smem, bars, blockIdx.x, a.comm_ctas);
     return;
   }
@@ -806,7 +872,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   volatile uint32_t* bail = tmem_holder + 1;
   uint32_t* warps_done = tmem_holder + 2;
 
-  if (a.times && cta_id == 0 && threadIdx.x == 0) a.times[0] = ptx::globaltimer_ns();
+  if (UCCL_TIMES(a) && cta_id == 0 && threadIdx.x == 0) a.times[0] = ptx::globaltimer_ns();
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_tiles = a.tiles_m * a.tiles_n;
@@ -846,7 +912,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         int mb, nb;
         tile_coords<16>(a, tile, a.tiles_m, 1, mb, nb);
         const bool own = mb >= a.a_local_lo && mb < a.a_local_hi;
-        if (a.a_ready && !(a.debug & 8) && !own) {
+        if (a.a_ready && !UCCL_DBG(a, 8) && !own) {
           if (!wait_flag_geq(a.a_ready + static_cast<size_t>(mb) * FLAG_STRIDE, a.a_ready_target, a.comm.timeout_ns,
                              a.comm.abort_flag)) {
             if (a.err) atomicCAS(a.err, 0u, 0x41470000u | static_cast<uint32_t>(mb));
@@ -907,10 +973,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         ptx::umma_commit(&tfull_bar[acc]);
       }
+    } else if (COMM != kCommNone && a.comm.go && cta_id == 0) {
+      prologue_barrier(a.comm, lane, a.err);  // the warp's idle lanes run the launch's rank barrier
     }
   } else if (warp == 6) {
     // ------------------------------------------------------------ forwarder (all-gather, spread mode)
-    if (COMM == kCommAllGather && a.a_spread && !(a.debug & 1)) {
+    int go_ok = 1;
+    if (COMM == kCommAllGather && a.a_spread && lane == 0) go_ok = wait_go(a.comm) ? 1 : 0;
+    go_ok = __shfl_sync(0xffffffffu, go_ok, 0);
+    if (COMM == kCommAllGather && a.a_spread && !UCCL_DBG(a, 1) && go_ok) {
       if (a.comm.a_full_mc) comm_allgather_push_mc(a, blockIdx.x, gridDim.x, lane);
       else if (lane == 0) comm_allgather_push<FWD_SLOT_BYTES, FWD_SLOTS, 2, 2>(a, smem + PIPE_BYTES, bars + 24, blockIdx.x, gridDim.x);
     }
@@ -920,6 +991,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint8_t* stage = smem + PIPE_BYTES + q * 2 * EPI_BUF_BYTES;
     uint32_t tcount = 0, stage_it = 0;
     int prev_mb = 0;
+    if (COMM == kCommReduceScatter) {
+      // no tile leaves for a peer before every rank has entered this launch
+      int g = 1;
+      if (lane == 0) g = wait_go(a.comm) ? 1 : 0;
+      if (!__shfl_sync(0xffffffffu, g, 0) && lane == 0) *bail = 1;
+      __syncwarp();
+    }
     for (int tile = cta_id; tile < num_tiles && !*bail; tile += gemm_ctas, ++tcount) {
       int mb, nb;
       tile_coords<16>(a, tile, a.tiles_m, 1, mb, nb);
@@ -947,9 +1025,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     ptx::tmem_dealloc(tmem_base, TMEM_COLS);
   }
   if (threadIdx.x == 0 && *bail && a.err) atomicCAS(a.err, 0u, 0x47454d4du);
-  if (a.times && cta_id == 0 && threadIdx.x == 0) a.times[1] = ptx::globaltimer_ns();
-  if (COMM == kCommReduceScatter && !*bail && !(a.debug & 1)) {
-    if (a.debug & 128) reduce_scatter_tail_direct(a, cta_id, gemm_ctas);
+  if (UCCL_TIMES(a) && cta_id == 0 && threadIdx.x == 0) a.times[1] = ptx::globaltimer_ns();
+  if (COMM == kCommReduceScatter && !*bail && !UCCL_DBG(a, 1)) {
+    if (UCCL_DBG(a, 128)) reduce_scatter_tail_direct(a, cta_id, gemm_ctas);
     else reduce_scatter_tail(a, smem, bars + 24, bail, cta_id, gemm_ctas, false);
   }
 }
@@ -975,7 +1053,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PIPE_BYTES + EPI_STAGE_BYTES);
   if (COMM == kCommAllGather && static_cast<int>(blockIdx.x) < a.comm_ctas) {
-    if (!(a.debug & 1) && threadIdx.x == 0)
+    if (!UCCL_DBG(a, 1) && threadIdx.x == 0 && wait_go(a.comm))
       comm_allgather_push<COPY_SLOT_BYTES, COPY_SLOTS, 4, 4>(a, smem, bars, blockIdx.x, a.comm_ctas);
     return;
   }
@@ -988,7 +1066,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   volatile uint32_t* bail = tmem_holder + 1;
   uint32_t* warps_done = tmem_holder + 2;
 
-  if (a.times && cta_id == 0 && threadIdx.x == 0) a.times[0] = ptx::globaltimer_ns();
+  if (UCCL_TIMES(a) && cta_id == 0 && threadIdx.x == 0) a.times[0] = ptx::globaltimer_ns();
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t crank = ptx::cluster_ctarank();  // 0 = leader
@@ -1038,7 +1116,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         tile_coords<8>(a, tile, tiles_m2, 2, mb2, nb);
         const int mb = 2 * mb2 + static_cast<int>(crank);  // this CTA's 128-row block
         const bool own = mb >= a.a_local_lo && mb < a.a_local_hi;
-        if (a.a_ready && !(a.debug & 8) && !own) {
+        if (a.a_ready && !UCCL_DBG(a, 8) && !own) {
           if (!wait_flag_geq(a.a_ready + static_cast<size_t>(mb) * FLAG_STRIDE, a.a_ready_target, a.comm.timeout_ns,
                              a.comm.abort_flag)) {
             if (a.err) atomicCAS(a.err, 0u, 0x41470000u | static_cast<uint32_t>(mb));
@@ -1097,10 +1175,15 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         ptx::umma_commit_pair(ptx::smem_u32(&tfull_bar[acc]));
         ptx::umma_commit_pair(tfull_peer + acc * 8);
       }
+    } else if (COMM != kCommNone && a.comm.go && cta_id == 0) {
+      prologue_barrier(a.comm, lane, a.err);  // the warp's idle lanes run the launch's rank barrier
     }
   } else if (warp == 6) {
     // ------------------------------------------------------------ forwarder (all-gather, spread mode)
-    if (COMM == kCommAllGather && a.a_spread && !(a.debug & 1)) {
+    int go_ok = 1;
+    if (COMM == kCommAllGather && a.a_spread && lane == 0) go_ok = wait_go(a.comm) ? 1 : 0;
+    go_ok = __shfl_sync(0xffffffffu, go_ok, 0);
+    if (COMM == kCommAllGather && a.a_spread && !UCCL_DBG(a, 1) && go_ok) {
       if (a.comm.a_full_mc) comm_allgather_push_mc(a, blockIdx.x, gridDim.x, lane);
       else if (lane == 0) comm_allgather_push<FWD_SLOT_BYTES, FWD_SLOTS, 2, 2>(a, smem + PIPE_BYTES, bars + 24, blockIdx.x, gridDim.x);
     }
@@ -1110,6 +1193,14 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     uint8_t* stage = smem + EPI_OFF + q * NBUF * EPI_BUF_BYTES;
     uint32_t tcount = 0, stage_it = 0;
     int prev_mb = 0;
+    if (COMM == kCommReduceScatter || COMM == kCommReduceScatterCe) {
+      // no tile leaves for a peer, and no flag is raised for a copy engine, before every rank has
+      // entered this launch
+      int g = 1;
+      if (lane == 0) g = wait_go(a.comm) ? 1 : 0;
+      if (!__shfl_sync(0xffffffffu, g, 0) && lane == 0) *bail = 1;
+      __syncwarp();
+    }
     for (int tile = pair_id; tile < num_tiles && !*bail; tile += pairs, ++tcount) {
       int mb2, nb;
       tile_coords<8>(a, tile, tiles_m2, 2, mb2, nb);
@@ -1167,9 +1258,9 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     ptx::tmem_dealloc_pair(tmem_base, TMEM_COLS);
   }
   if (threadIdx.x == 0 && *bail && a.err) atomicCAS(a.err, 0u, 0x47454d32u);
-  if (a.times && cta_id == 0 && threadIdx.x == 0) a.times[1] = ptx::globaltimer_ns();
-  if ((COMM == kCommReduceScatter || COMM == kCommReduceScatterCe) && !*bail && !(a.debug & 1)) {
-    if (COMM == kCommReduceScatter && (a.debug & 128)) reduce_scatter_tail_direct(a, cta_id, a.gemm_ctas);
+  if (UCCL_TIMES(a) && cta_id == 0 && threadIdx.x == 0) a.times[1] = ptx::globaltimer_ns();
+  if ((COMM == kCommReduceScatter || COMM == kCommReduceScatterCe) && !*bail && !UCCL_DBG(a, 1)) {
+    if (COMM == kCommReduceScatter && UCCL_DBG(a, 128)) reduce_scatter_tail_direct(a, cta_id, a.gemm_ctas);
     else reduce_scatter_tail(a, smem, bars + 24, bail, cta_id, a.gemm_ctas, COMM == kCommReduceScatterCe);
   }
 }

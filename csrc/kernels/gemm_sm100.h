@@ -27,6 +27,11 @@ struct GemmFusion {
   int comm_ctas = 0;         // all-gather: CTAs that move data (reduce-scatter reserves none)
   uint64_t timeout_ns = 0;
   uint32_t* abort_flag = nullptr;
+  // rank barrier folded into the launch (all three null: the caller ran a barrier kernel itself):
+  // every rank's arena, this rank's epoch counters, and a local word that is zero at launch
+  char* const* arena_peer = nullptr;
+  uint32_t* epochs = nullptr;
+  uint32_t* go = nullptr;
   int rows_per_rank = 0;
   // all-gather: my shard, every rank's A_full (peer-mapped) and every rank's arrival counters
   // (zeroed before the launch); a_inplace: the shard already sits in my A_full

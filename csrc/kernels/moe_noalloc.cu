@@ -179,6 +179,8 @@ extern "C" ucclResult_t ucclMoeDispatchLocalNoAlloc(const void* x, const int32_t
                   static_cast<long>(tokens) * topk);
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(recvX) | reinterpret_cast<uintptr_t>(recvMeta)) & 15)
     return refuse(ucclInvalidArgument, "x, recvX and recvMeta must be 16-byte aligned");
+  if ((reinterpret_cast<uintptr_t>(recvScale) | reinterpret_cast<uintptr_t>(topkIdx) | reinterpret_cast<uintptr_t>(recvCount)) & 3)
+    return refuse(ucclInvalidArgument, "recvScale, topkIdx and recvCount must be 4-byte aligned");
   unsigned char* scratch = nullptr;
   ucclResult_t r = scratchForCurrentDevice(&scratch);
   if (r != ucclSuccess) return r;

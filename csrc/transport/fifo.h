@@ -36,7 +36,7 @@ struct alignas(64) ConnFifo {
   alignas(64) FifoEntry entries[UCCL_STEPS];
 };
 
-// Host-side accessors (the device-side twins are in kernels/net_prims.cuh).
+// Host-side accessors (the device side uses ld.acquire.sys / st.release.sys, kernels/net_ring.cu).
 inline uint64_t fifoLoadAcquire(const uint64_t* p) { return __atomic_load_n(p, __ATOMIC_ACQUIRE); }
 inline void fifoStoreRelease(uint64_t* p, uint64_t v) { __atomic_store_n(p, v, __ATOMIC_RELEASE); }
 

@@ -50,13 +50,16 @@ def test_rejects_sizes_beyond_the_built_in_scratch():
     assert rc == 3 and b"hidden" in lib.ucclNoAllocLastError()
     rc = lib.ucclMoeDispatchLocalNoAlloc(one, one, 16, 1024, 8, 4, one, one, one, one, 63, None)
     assert rc == 3 and b"rowsCapacity" in lib.ucclNoAllocLastError()
+    odd = ctypes.c_void_p(18)  # a scale pointer that a float store cannot use
+    rc = lib.ucclMoeDispatchLocalNoAlloc(one, one, 16, 1024, 8, 4, one, odd, one, one, 64, None)
+    assert rc == 3 and b"4-byte aligned" in lib.ucclNoAllocLastError()
 
 
 @pytest.mark.gpu
 def test_matches_the_regular_dispatch_twice_in_a_row():
     os.environ.setdefault("UCCL_BOOTSTRAP_IFNAME", "lo")
     from unified_ccl_b200 import Communicator
-    from unified_ccl_b200.parallel import MoeDispatcher
+    from unified_ccl_b200.parallel import MoeDispatcher, quantize_fp8_block128
 
     lib = _lib()
     torch.cuda.set_device(0)
@@ -90,5 +93,14 @@ def test_matches_the_regular_dispatch_twice_in_a_row():
         assert torch.equal(got[2], want[2])                      # same (token, expert, k, 1) descriptors
         assert torch.equal(got[0], want[0])                      # same fp8 payload, bit for bit
         assert torch.allclose(got[1], want[1], rtol=1e-6, atol=0)  # same scales
+        # and both equal the fp32 restatement of the cast (amax / 448 per 128 elements, e4m3 rounding)
+        src_rows = x.float().cpu()[got[2][:, 0].long()]
+        q_ref, s_ref = quantize_fp8_block128(src_rows)
+        assert torch.allclose(got[1], s_ref, rtol=1e-6, atol=0)
+        deq = got[0].view(torch.float8_e4m3fn).float().view(count, hidden // 128, 128) * got[1].unsqueeze(-1)
+        ref = q_ref.float().view(count, hidden // 128, 128) * s_ref.unsqueeze(-1)
+        amax = src_rows.view(count, hidden // 128, 128).abs().amax(-1, keepdim=True)
+        assert ((deq - ref).abs() <= 0.0625 * amax + 1e-6).all()  # at most one fp8 step apart, never more
+        assert (got[0] != q_ref.view(torch.uint8)).float().mean().item() < 1e-3  # and bit-identical almost everywhere
     disp.close()
     comm.destroy()
