@@ -122,6 +122,8 @@ install: $(LIB)
 	install -d $(DESTDIR)$(PREFIX)/lib $(DESTDIR)$(PREFIX)/include
 	install -m 755 $(LIB) $(DESTDIR)$(PREFIX)/lib/libuccl.so
 	install -m 644 $(PUBLIC_HEADERS) $(DESTDIR)$(PREFIX)/include/
+	install -d $(DESTDIR)$(PREFIX)/share/uccl/tuning
+	install -m 644 $(PKG)/tuning/*.json $(DESTDIR)$(PREFIX)/share/uccl/tuning/
 ifeq ($(UCCL_BUILD_PLUGIN),1)
 	install -m 755 $(PLUGIN) $(DESTDIR)$(PREFIX)/lib/ 2>/dev/null || true
 endif

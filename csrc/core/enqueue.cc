@@ -497,8 +497,17 @@ ucclResult_t executeOp(const CollOp& op) {
       (op.kind == ucclCollAllReduce || op.kind == ucclCollAllGather || op.kind == ucclCollReduceScatter))
     return enqueueCopyEngine(c, op);
   if (ch.algo == ucclAlgoRing &&
-      (op.kind == ucclCollAllReduce || op.kind == ucclCollAllGather || op.kind == ucclCollReduceScatter))
-    return enqueueRing(c, op, ch.proto == ucclProtoLL128 ? ucclProtoLL128 : ucclProtoSimple, ch.blocks);
+      (op.kind == ucclCollAllReduce || op.kind == ucclCollAllGather || op.kind == ucclCollReduceScatter)) {
+    if (reducible(op.dtype)) return enqueueRing(c, op, ch.proto == ucclProtoLL128 ? ucclProtoLL128 : ucclProtoSimple, ch.blocks);
+    // copy-only element types (fp8, raw bytes) ride the ring as 4- or 2-byte words; an odd byte
+    // count takes the direct kernels below
+    if (op.kind == ucclCollAllGather && (chunk % 2) == 0) {
+      CollOp w = op;
+      w.dtype = (chunk % 4) == 0 ? ucclFloat32 : ucclFloat16;
+      w.count = chunk / dataTypeSize(w.dtype);
+      return enqueueRing(c, w, ch.proto == ucclProtoLL128 ? ucclProtoLL128 : ucclProtoSimple, ch.blocks);
+    }
+  }
 
   switch (op.kind) {
     case ucclCollAllReduce:

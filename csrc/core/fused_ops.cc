@@ -305,11 +305,11 @@ extern "C" ucclResult_t ucclAllGatherGemm(const void* xShard, void* xFull, const
   }
   commCount(c, ucclCollAllGather, static_cast<size_t>(M) * K * 2, ucclAlgoOneShot);
   f.a_spread = agMode == 3 ? 1 : 0;
-  // Forwarder warps store through the switch when xFull has a multicast alias: one store stream
+  // Forwarder warps (or the warps of the communication CTAs) store through the switch when xFull has a multicast alias: one store stream
   // that the switch replicates, instead of nranks - 1 unicast copies.  Between two GPUs there is
   // nothing to replicate and plain peer stores are faster.  UCCL_FUSED_AG_MC=0/1 overrides.
-  bool viaSwitch = f.a_spread && sf.seg->mc != nullptr && n > 2 && c->forcedAlgo != ucclAlgoTwoShot && c->forcedAlgo != ucclAlgoOneShot;
-  if (const char* e = getenv("UCCL_FUSED_AG_MC")) viaSwitch = f.a_spread && sf.seg->mc != nullptr && atoi(e) != 0;
+  bool viaSwitch = sf.seg->mc != nullptr && n > 2 && c->forcedAlgo != ucclAlgoTwoShot && c->forcedAlgo != ucclAlgoOneShot;
+  if (const char* e = getenv("UCCL_FUSED_AG_MC")) viaSwitch = sf.seg->mc != nullptr && atoi(e) != 0;
   if (viaSwitch) f.a_full_mc = sf.seg->mc + sf.off;
   // The kernel reads my rows from the shard; they reach xFull through the switch with everybody
   // else's copy, or else a copy engine puts them there meanwhile.

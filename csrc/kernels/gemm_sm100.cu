@@ -237,7 +237,7 @@ ucclResult_t launchGemmBf16(const GemmLaunch& g, const GemmFusion* f, cudaStream
       const size_t blkBytes = static_cast<size_t>(gemm::BM) * g.K * 2;
       a.a_spread = (!f->a_external && f->a_spread) ? 1 : 0;
       if (f->a_external) a.a_ready_target = 1;
-      else if (a.a_spread) a.a_ready_target = static_cast<uint32_t>((blkBytes + gemm::FWD_SLOT_BYTES - 1) / gemm::FWD_SLOT_BYTES);
+      else if (a.a_spread || f->a_full_mc) a.a_ready_target = static_cast<uint32_t>((blkBytes + gemm::FWD_SLOT_BYTES - 1) / gemm::FWD_SLOT_BYTES);
       else a.a_ready_target = static_cast<uint32_t>((blkBytes + gemm::COPY_SLOT_BYTES - 1) / gemm::COPY_SLOT_BYTES);
       a.a_local_lo = f->rank * blk_per_rank;
       a.a_local_hi = a.a_local_lo + blk_per_rank;

@@ -859,6 +859,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PIPE_BYTES + EPI_STAGE_BYTES);
   if (COMM == kCommAllGather && static_cast<int>(blockIdx.x) < a.comm_ctas) {
+    if (a.comm.a_full_mc) {
+      // through the switch: every warp of the communication CTAs is a pusher of its own
+      const int w = threadIdx.x >> 5, nw = blockDim.x >> 5, l = threadIdx.x & 31;
+      int g = 1;
+      if (l == 0) g = wait_go(a.comm) ? 1 : 0;
+      g = __shfl_sync(0xffffffffu, g, 0);
+      if (g && !UCCL_DBG(a, 1)) comm_allgather_push_mc(a, static_cast<int>(blockIdx.x) * nw + w, a.comm_ctas * nw, l);
+      return;
+    }
     if (!UCCL_DBG(a, 1) && threadIdx.x == 0 && wait_go(a.comm))
       comm_allgather_push<COPY_SLOT_BYTES, COPY_SLOTS, 4, 4>(a, smem, bars, blockIdx.x, a.comm_ctas);
     return;
@@ -1053,6 +1062,15 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PIPE_BYTES + EPI_STAGE_BYTES);
   if (COMM == kCommAllGather && static_cast<int>(blockIdx.x) < a.comm_ctas) {
+    if (a.comm.a_full_mc) {
+      // through the switch: every warp of the communication CTAs is a pusher of its own
+      const int w = threadIdx.x >> 5, nw = blockDim.x >> 5, l = threadIdx.x & 31;
+      int g = 1;
+      if (l == 0) g = wait_go(a.comm) ? 1 : 0;
+      g = __shfl_sync(0xffffffffu, g, 0);
+      if (g && !UCCL_DBG(a, 1)) comm_allgather_push_mc(a, static_cast<int>(blockIdx.x) * nw + w, a.comm_ctas * nw, l);
+      return;
+    }
     if (!UCCL_DBG(a, 1) && threadIdx.x == 0 && wait_go(a.comm))
       comm_allgather_push<COPY_SLOT_BYTES, COPY_SLOTS, 4, 4>(a, smem, bars, blockIdx.x, a.comm_ctas);
     return;

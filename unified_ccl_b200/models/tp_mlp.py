@@ -48,8 +48,20 @@ class TensorParallelMLP:
     __call__ = forward
 
     # candidates of autotune(): (all-gather mode, communication CTAs or copy-engine lanes, chunks per peer)
-    AG_CANDIDATES = (("ce", 0, 1), ("ce", 0, 2), ("ce", 0, 4), ("ce", 1, 2), ("ce", 2, 2), ("ce", 2, 4), ("ce", 3, 2),
-                     ("spread", 0, 0), ("kernel", 8, 0), ("kernel", 16, 0), ("kernel", 24, 0))
+    # "spread" stores through the switch where the buffer has a multicast alias and there are more than two
+    # ranks; "spread_uc" is the same forwarder warp with unicast bulk copies
+    AG_CANDIDATES = (("ce", 0, 1), ("ce", 0, 2), ("ce", 0, 4), ("ce", 1, 2), ("ce", 2, 2), ("ce", 1, 4),
+                     ("spread", 0, 0), ("spread_uc", 0, 0), ("kernel", 4, 0), ("kernel", 8, 0), ("kernel", 16, 0))
+
+    def _apply_ag(self, mode, ctas, chunks):
+        import os
+
+        if mode == "spread_uc":
+            os.environ["UCCL_FUSED_AG_MC"] = "0"
+            mode = "spread"
+        else:
+            os.environ.pop("UCCL_FUSED_AG_MC", None)
+        self.comm.set_fused_options(mode, ctas, chunks)
 
     def autotune(self, x_shard: torch.Tensor, iters: int = 3, candidates=None):
         """Times the all-gather -> GEMM half of the block under each candidate setting (CUDA events,
@@ -64,7 +76,7 @@ class TensorParallelMLP:
         stream = torch.cuda.current_stream(self.h.device)
         for i, (mode, ctas, chunks) in enumerate(cands):
             try:
-                self.comm.set_fused_options(mode, ctas, chunks)
+                self._apply_ag(mode, ctas, chunks)
                 allgather_gemm(self.comm, x_shard, self.x_full, self.w_gate_up, out=self.h, swiglu=True)  # warm-up
                 s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 s.record(stream)
@@ -81,7 +93,7 @@ class TensorParallelMLP:
         stream.synchronize()
         avg = (times / self.tp).tolist()
         best = min(range(len(cands)), key=lambda i: avg[i])
-        self.comm.set_fused_options(*cands[best])
+        self._apply_ag(*cands[best])
         self.ag_choice = cands[best]
         return {cands[i]: round(avg[i], 1) for i in range(len(cands))}
 
