@@ -84,8 +84,8 @@ def main():
     # untimed: the same for the GEMM -> reduce-scatter half (epilogue stores or copy engines)
     if world > 1 and not os.environ.get("UCCL_FUSED_RS"):
         mlp(x_dev)  # fills the activations the second half works on
-        autotune_rs = {"%s/chunks%d" % k: v for k, v in mlp.autotune_rs().items()}
-        autotune_rs["chosen"] = "%s/chunks%d" % mlp.rs_choice
+        autotune_rs = {"%s/%d" % k: v for k, v in mlp.autotune_rs().items()}  # kernel/<reducer CTAs> or ce/<chunks>
+        autotune_rs["chosen"] = "%s/%d" % mlp.rs_choice
 
     def barrier():
         if world > 1:

@@ -105,6 +105,7 @@ struct Comm {
   size_t rsSendBytes = 0;
   void* rsCtl = nullptr;              // u32 counts at +0, u64 flags at +1024
   int fusedRsMode = 0, fusedRsChunks = 0;  // ucclCommSetFusedRsOptions (0 = default)
+  int fusedRsReducers = 0;                  // ucclCommSetFusedRsReducers: CTAs that only sum
   void* onesDev = nullptr;            // 32-bit ones at the GEMM flag stride (source of copy-engine flag writes)
 
   // network path

@@ -242,7 +242,7 @@ extern "C" ucclResult_t ucclAllGatherGemm(const void* xShard, void* xFull, const
     commSetError(c, "all-gather GEMM needs M / nranks to be a multiple of 128 (M=%d, nranks=%d)", M, n);
     return ucclInvalidArgument;
   }
-  if (M / 128 >= kGemmMaxRowBlocks) return ucclInvalidArgument;  // one more line holds the launch's go flag
+  if (M / 128 + 2 > kGemmMaxRowBlocks) return ucclInvalidArgument;  // two more lines hold the launch's go flag and work counter
   Sym sf;
   if (!symOf(c, xFull, static_cast<size_t>(M) * K * 2, &sf)) {
     commSetError(c, "xFull must come from ucclMemAlloc");
@@ -348,7 +348,7 @@ extern "C" ucclResult_t ucclGemmReduceScatter(const void* A, const void* W, void
     commSetError(c, "GEMM reduce-scatter needs M / nranks to be a multiple of 128 and N a multiple of 8");
     return ucclInvalidArgument;
   }
-  if (M / 128 >= kGemmMaxRowBlocks) return ucclInvalidArgument;  // one more line holds the launch's go flag
+  if (M / 128 + 2 > kGemmMaxRowBlocks) return ucclInvalidArgument;  // two more lines hold the launch's go flag and work counter
   Sym sp;
   if (!symOf(c, cPartial, static_cast<size_t>(M) * N * 2, &sp)) {
     commSetError(c, "cPartial must come from ucclMemAlloc");
@@ -358,9 +358,17 @@ extern "C" ucclResult_t ucclGemmReduceScatter(const void* A, const void* W, void
   // partial sums of this rank's rows.  The counters start at zero, and the barrier also orders
   // this launch's remote writes after every rank's previous use of its staging buffer.
   uint32_t* done = reinterpret_cast<uint32_t*>(c->arena->local + kArenaGemmDoneOff);
-  if (cudaMemsetAsync(done, 0, kGemmFlagStrideBytes * (M / 128 + 1), s) != cudaSuccess) return ucclSystemError;
+  if (cudaMemsetAsync(done, 0, kGemmFlagStrideBytes * (M / 128 + 2), s) != cudaSuccess) return ucclSystemError;
   const bool fold = foldBarrier();
+  // the two lines after the last counter: the launch's go flag and the work counter of its summing tail
   uint32_t* go = done + static_cast<size_t>(M / 128) * (kGemmFlagStrideBytes / 4);
+  uint32_t* tailNext = go + kGemmFlagStrideBytes / 4;
+  // CTAs that only sum (UCCL_FUSED_RS_REDUCERS, else the communicator's option): when the links, not
+  // the tensor cores, set the pace of the main loop, a few SMs taken from the GEMM cost nothing and
+  // the summing no longer waits for the last tile
+  int reducers = c->fusedRsReducers;
+  if (const char* e = getenv("UCCL_FUSED_RS_REDUCERS")) reducers = atoi(e);
+  if (reducers < 0 || reducers > 64) reducers = 0;
   const int rsChunks = fusedRsCeChunks(c, M / n / 128);
   if (rsChunks > 0) {
     // ---- copy engines carry the slabs (see reduceScatterPushCopies)
@@ -400,6 +408,8 @@ extern "C" ucclResult_t ucclGemmReduceScatter(const void* A, const void* W, void
       f.go = go;
     }
     f.role = 3;
+    f.tail_next = tailNext;
+    f.rs_reducers = reducers;
     f.rank = c->localRank;
     f.nranks = n;
     f.timeout_ns = c->dev.timeoutNs;
@@ -440,6 +450,8 @@ extern "C" ucclResult_t ucclGemmReduceScatter(const void* A, const void* W, void
     f.go = go;
   }
   f.role = 2;
+  f.tail_next = tailNext;
+  f.rs_reducers = reducers;
   f.rank = c->localRank;
   f.nranks = n;
   f.timeout_ns = c->dev.timeoutNs;

@@ -620,6 +620,13 @@ extern "C" ucclResult_t ucclCommSetFusedRsOptions(ucclComm_t comm, int rsMode, i
   return ucclSuccess;
 }
 
+extern "C" ucclResult_t ucclCommSetFusedRsReducers(ucclComm_t comm, int reducerCtas) {
+  Comm* c = toComm(comm);
+  if (!commValid(c) || reducerCtas < 0 || reducerCtas > 64) return ucclInvalidArgument;
+  c->fusedRsReducers = reducerCtas;
+  return ucclSuccess;
+}
+
 extern "C" ucclResult_t ucclCommSetBlocks(ucclComm_t comm, int blocks) {
   Comm* c = toComm(comm);
   if (!commValid(c) || blocks < 0 || blocks > kMaxBlocks) return ucclInvalidArgument;

@@ -4,6 +4,7 @@
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
+#include <strings.h>
 
 #include <algorithm>
 
@@ -262,6 +263,7 @@ ucclResult_t launchGemmBf16(const GemmLaunch& g, const GemmFusion* f, cudaStream
       c.own_target = static_cast<uint32_t>(a.tiles_n * 4);
       c.rs_out = static_cast<char*>(f->rs_out);
       c.rs_ldo = f->rs_ldo;
+      c.tail_next = f->tail_next;
       a.m_order = 4;
     } else {
       for (int i = 0; i < f->nranks; ++i) {
@@ -274,10 +276,30 @@ ucclResult_t launchGemmBf16(const GemmLaunch& g, const GemmFusion* f, cudaStream
       c.done_target = static_cast<uint32_t>(f->nranks * a.tiles_n);
       c.rs_out = static_cast<char*>(f->rs_out);
       c.rs_ldo = f->rs_ldo;
+      c.tail_next = f->tail_next;
       a.m_order = (a.debug & 4) ? 0 : 2;
     }
   }
   a.comm_ctas = comm_ctas;
+
+  // Epilogue through shared memory + TMA stores: whole 128-byte lines instead of one 16-byte piece
+  // per lane and row.  Needs 64-column boxes to tile the output exactly; the unicast forwarder warp
+  // of the all-gather fusion uses the same staging area, so that mode keeps the direct stores.
+  // UCCL_GEMM_EPI=lsu|tma overrides.
+  {
+    const int outN = g.epilogue == gemm::kEpiSwiGLU ? g.N / 2 : g.N;
+    bool tma = outN % 64 == 0 && role != gemm::kCommReduceScatter && !(a.a_spread && !a.comm.a_full_mc);
+    if (const char* e = getenv("UCCL_GEMM_EPI")) {
+      if (!strcasecmp(e, "lsu")) tma = false;
+    }
+    if (tma) {
+      if (!makeTensorMap(&pm.m[gemm::kMaxPeers], g.C, g.M, outN, g.ldc, 64, 32)) return ucclSystemError;
+      if (role == gemm::kCommReduceScatterCe &&
+          !makeTensorMap(&pm.m[0], f->stage_peer[f->rank], static_cast<uint64_t>(f->nranks) * f->rows_per_rank, g.N, g.N, 64, 32))
+        return ucclSystemError;
+      a.epi_tma = 1;
+    }
+  }
 
   const bool fusedOk = role == 0 || (f->rows_per_rank % (2 * gemm::BM) == 0);
   cudaError_t e;
@@ -291,9 +313,14 @@ ucclResult_t launchGemmBf16(const GemmLaunch& g, const GemmFusion* f, cudaStream
     a.comm_ctas = comm_ctas;
     int maxPairs = maxResidentPairs();
     if (g.max_ctas > 0) maxPairs = std::min(maxPairs, g.max_ctas / 2);
-    int pairs = std::max(1, std::min(maxPairs - comm_ctas / 2, tiles2));
+    // reducer CTAs (reduce-scatter only, and only with the shared work counter) come out of the
+    // resident budget: they must run from the start, next to the GEMM CTAs
+    int reducers = 0;
+    if ((role == gemm::kCommReduceScatter || role == gemm::kCommReduceScatterCe) && f->tail_next && f->rs_reducers > 0)
+      reducers = std::min(f->rs_reducers & ~1, maxPairs & ~1);  // whole clusters, at most half of the resident CTAs
+    int pairs = std::max(1, std::min(maxPairs - comm_ctas / 2 - reducers / 2, tiles2));
     a.gemm_ctas = 2 * pairs;
-    const int grid = a.gemm_ctas + comm_ctas;
+    const int grid = a.gemm_ctas + comm_ctas + reducers;
     if (g.epilogue == gemm::kEpiSwiGLU) {
       if (role == gemm::kCommAllGather) e = launchPairT<gemm::kEpiSwiGLU, gemm::kCommAllGather>(tmA, tmB, pm, a, grid, stream);
       else e = launchPairT<gemm::kEpiSwiGLU, gemm::kCommNone>(tmA, tmB, pm, a, grid, stream);
@@ -305,8 +332,10 @@ ucclResult_t launchGemmBf16(const GemmLaunch& g, const GemmFusion* f, cudaStream
     }
   } else {
     const int tiles = a.tiles_m * a.tiles_n;
-    a.gemm_ctas = std::max(1, std::min(sms - comm_ctas, tiles));
-    const int grid = a.gemm_ctas + comm_ctas;
+    int reducers = 0;
+    if (role == gemm::kCommReduceScatter && f->tail_next && f->rs_reducers > 0) reducers = std::min(f->rs_reducers, sms / 2);
+    a.gemm_ctas = std::max(1, std::min(sms - comm_ctas - reducers, tiles));
+    const int grid = a.gemm_ctas + comm_ctas + reducers;
     if (g.epilogue == gemm::kEpiSwiGLU) {
       if (role == gemm::kCommAllGather) e = launchT<gemm::kEpiSwiGLU, gemm::kCommAllGather>(tmA, tmB, pm, a, grid, stream);
       else e = launchT<gemm::kEpiSwiGLU, gemm::kCommNone>(tmA, tmB, pm, a, grid, stream);

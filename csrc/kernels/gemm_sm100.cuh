@@ -130,6 +130,7 @@ struct CommArgs {
   uint32_t* done_peer[kMaxPeers] = {};  // every rank's per-row-block counters, zero at launch
   uint32_t done_target = 0;             // nranks * column tiles
   char* rs_out = nullptr;               // [rows_per_rank, N] bf16
+  uint32_t* tail_next = nullptr;        // local, zero at launch: next unit of the summing tail to hand out (nullptr: static split)
   int rs_ldo = 0;
 };
 
@@ -156,6 +157,7 @@ struct Args {
   int a_local_lo, a_local_hi;  // row blocks in [lo, hi) need no wait (my own rows)
   int a_spread;             // all-gather: warp 6 of every GEMM CTA forwards a share of the shard
   int a_own_shard;          // all-gather: read my own rows through pm.m[0] (the shard) instead of A
+  int epi_tma;              // epilogue writes C through shared memory + TMA stores (pm.m[kMaxPeers] maps C)
   uint32_t* err;            // error word (mapped or device memory); 0 = ok
   unsigned long long* times;  // optional: CTA 0 records globaltimer stamps here (profiling aid)
   int debug;                // experiment switches: 1 no communication work, 2 no remote tile stores,
@@ -628,8 +630,18 @@ __device__ void reduce_scatter_tail(const Args& a, uint8_t* smem, uint64_t* tbar
   }
   const uint32_t P = static_cast<uint32_t>(blkBytes / pieces);
   const int units = bpr * pieces;
-  int myUnits = 0;
-  for (int u = cta; u < units; u += nctas) ++myUnits;
+  // Units (one piece of one row block) are handed out in block order, which is the order in which
+  // the blocks complete: from a shared counter when the launch has one, so that reducer CTAs that
+  // start at once and GEMM CTAs that join when their tiles are done share the work; else by a
+  // static stride over the CTAs.
+  __shared__ int s_unit[3];
+  int claimed = 0;  // thread 0: claims made so far (static split)
+  auto claim = [&]() -> int {
+    int u;
+    if (c.tail_next) u = static_cast<int>(atomicAdd(c.tail_next, 1u));
+    else u = cta + (claimed++) * nctas;
+    return u < units ? u : -1;
+  };
   const int first_blk = c.rank * bpr;
   uint32_t* done = c.done_peer[c.rank] + static_cast<size_t>(first_blk) * FLAG_STRIDE;
   // blocks [0, readyUpTo) are known complete; counters are read relaxed and one fence follows
@@ -674,8 +686,10 @@ __device__ void reduce_scatter_tail(const Args& a, uint8_t* smem, uint64_t* tbar
     ptx::fence_proxy_async();  // the staged tiles were written by the ranks' TMA stores
   }
   __syncthreads();
-  auto issue = [&](int i) {  // thread 0: loads of my i-th unit
-    const int u = cta + i * nctas;
+  auto issue = [&](int i) {  // thread 0: claims my i-th unit and starts its loads
+    const int u = claim();
+    s_unit[i % TSTAGES] = u;
+    if (u < 0) return;
     const int b = u / pieces, part = u - b * pieces;
     if (b >= readyUpTo) {
       if (!await(b)) {
@@ -694,22 +708,30 @@ __device__ void reduce_scatter_tail(const Args& a, uint8_t* smem, uint64_t* tbar
                      c.stage_local + static_cast<size_t>(p) * slotBytes + off, P, &tbars[st]);
   };
   if (threadIdx.x == 0) {
-    for (int i = 0; i < TSTAGES - 1 && i < myUnits && !*bail; ++i) issue(i);
+    for (int i = 0; i < TSTAGES - 1; ++i) {
+      if (!*bail) issue(i);
+      else s_unit[i] = -1;
+    }
   }
+  __syncthreads();
   const int nv = static_cast<int>(P >> 4);
   const bool contig = static_cast<size_t>(c.rs_ldo) * 2 == rowBytes;
   const size_t outRowBytes = static_cast<size_t>(c.rs_ldo) * 2;
   const int warp = threadIdx.x >> 5;
   if (UCCL_TIMES(a) && cta == 0 && threadIdx.x == 0) a.times[2] = ptx::globaltimer_ns();
-  for (int i = 0; i < myUnits; ++i) {
+  for (int i = 0;; ++i) {
     // stage (i + 2) % 3 was consumed in iteration i - 1, which ended with a CTA barrier
-    if (threadIdx.x == 0 && i + TSTAGES - 1 < myUnits && !*bail) issue(i + TSTAGES - 1);
+    if (threadIdx.x == 0) {
+      if (!*bail) issue(i + TSTAGES - 1);
+      else s_unit[(i + TSTAGES - 1) % TSTAGES] = -1;
+    }
     const int st = i % TSTAGES;
+    const int u = s_unit[st];  // written two iterations (two CTA barriers) ago
+    if (u < 0) break;  // same value in every thread
     bool ok = true;
     if (warp != 0) ok = ptx::mbar_wait_bounded(&tbars[st], (i / TSTAGES) & 1, bail);
     if (UCCL_TIMES(a) && cta == 0 && threadIdx.x == 32 && i < 8) a.times[16 + 2 * i] = ptx::globaltimer_ns();
     if (warp != 0 && ok) {
-      const int u = cta + i * nctas;
       const int b = u / pieces, part = u - b * pieces;
       const size_t flat0 = static_cast<size_t>(b) * blkBytes + static_cast<size_t>(part) * P;
       const uint32_t row0 = static_cast<uint32_t>(flat0 / rowBytes);
@@ -731,10 +753,81 @@ __device__ void reduce_scatter_tail(const Args& a, uint8_t* smem, uint64_t* tbar
 
 // ------------------------------------------------------------------ epilogue of one tile, one warp
 // `taddr` addresses this warp's 32 TMEM lanes of the accumulator; `mb` is the 128-row block.
+// 64 columns x 32 rows of bf16 (eight 16-byte pieces per lane) -> 128-byte-swizzled staging buffer
+// -> one TMA store at (col0, row0) of `map`.  One bulk group per call.
+template <int NBUF>
+__device__ __forceinline__ void stage_and_store(const CUtensorMap* map, const uint4 (&v)[8], int col0, int row0, bool inside,
+                                                int lane, uint8_t* stage, uint32_t& stage_it) {
+  uint8_t* buf = stage + (stage_it % NBUF) * EPI_BUF_BYTES;
+  ++stage_it;
+  if (lane == 0) ptx::tma_store_wait_read<NBUF - 1>();  // the store that last used this buffer has read it
+  __syncwarp();
+  uint8_t* myrow = buf + lane * 128;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) *reinterpret_cast<uint4*>(myrow + ((k ^ (lane & 7)) << 4)) = v[k];  // 128-byte swizzle
+  ptx::fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0 && inside) ptx::tma_store_2d(map, buf, col0, row0);
+  if (lane == 0) ptx::tma_store_commit();
+}
+
+// `cmap` != nullptr: C is written through shared memory and TMA stores (whole 128-byte lines, rows
+// and columns beyond the matrix clipped by the copy engine) at rows crow0 ... of that map; else
+// every lane stores its own row with 16-byte stores.
 template <int EPI, int COMM, int NBUF>
 __device__ __forceinline__ void epilogue_tile(const Args& a, const PeerMaps& pm, uint32_t taddr, int mb, int nb, int q,
-                                              int lane, uint8_t* stage, uint32_t& stage_it, __nv_bfloat16* cbase) {
+                                              int lane, uint8_t* stage, uint32_t& stage_it, __nv_bfloat16* cbase,
+                                              const CUtensorMap* cmap = nullptr, int crow0 = 0) {
   const int row = mb * BM + q * 32 + lane;
+  if (COMM != kCommReduceScatter && cmap) {
+    if (EPI == kEpiStore) {
+#pragma unroll 1
+      for (int g = 0; g < BN / 64; ++g) {
+        uint32_t r0[32], r1[32];
+        ptx::tmem_ld_32x32b_x32(taddr + g * 64, r0);
+        ptx::tmem_ld_32x32b_x32(taddr + g * 64 + 32, r1);
+        ptx::tmem_ld_wait();
+        uint4 v[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t* s = k < 4 ? &r0[8 * k] : &r1[8 * (k - 4)];
+          v[k].x = ptx::pack_bf16x2(__uint_as_float(s[0]), __uint_as_float(s[1]));
+          v[k].y = ptx::pack_bf16x2(__uint_as_float(s[2]), __uint_as_float(s[3]));
+          v[k].z = ptx::pack_bf16x2(__uint_as_float(s[4]), __uint_as_float(s[5]));
+          v[k].w = ptx::pack_bf16x2(__uint_as_float(s[6]), __uint_as_float(s[7]));
+        }
+        const int col0 = nb * BN + g * 64;
+        stage_and_store<NBUF>(cmap, v, col0, crow0, col0 < a.N && crow0 < a.M, lane, stage, stage_it);
+      }
+    } else {
+      // gate columns [0,128) and up columns [128,256) of the accumulator -> 128 output columns
+      const int out_n = a.N / 2;
+#pragma unroll 1
+      for (int g = 0; g < BN / 128; ++g) {
+        uint4 v[8];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t gt[32], up[32];
+          ptx::tmem_ld_32x32b_x32(taddr + g * 64 + h * 32, gt);
+          ptx::tmem_ld_32x32b_x32(taddr + BN / 2 + g * 64 + h * 32, up);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float o[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o[e] = silu_f(__uint_as_float(gt[8 * j + e])) * __uint_as_float(up[8 * j + e]);
+            v[h * 4 + j].x = ptx::pack_bf16x2(o[0], o[1]);
+            v[h * 4 + j].y = ptx::pack_bf16x2(o[2], o[3]);
+            v[h * 4 + j].z = ptx::pack_bf16x2(o[4], o[5]);
+            v[h * 4 + j].w = ptx::pack_bf16x2(o[6], o[7]);
+          }
+        }
+        const int col0 = nb * (BN / 2) + g * 64;
+        stage_and_store<NBUF>(cmap, v, col0, crow0, col0 < out_n && crow0 < a.M, lane, stage, stage_it);
+      }
+    }
+    return;
+  }
   if (COMM == kCommReduceScatter) {
     // bf16 tile -> swizzled shared memory -> TMA store into the owner's staging slot [my rank]
     const int rpr = a.comm.rows_per_rank;
@@ -873,6 +966,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     return;
   }
   const int cta_id = static_cast<int>(blockIdx.x) - a.comm_ctas;
+  if (COMM == kCommReduceScatter && cta_id >= a.gemm_ctas) {
+    // reducer CTA: sums the staged copies of this rank's row blocks as they complete, from the start
+    volatile uint32_t* rbail = reinterpret_cast<volatile uint32_t*>(bars + 28);
+    if (threadIdx.x == 0) *rbail = 0;
+    __syncthreads();
+    reduce_scatter_tail(a, smem, bars + 24, rbail, cta_id, a.gemm_ctas, false);
+    return;
+  }
   uint64_t* full_bar = bars;                     // [STAGES]
   uint64_t* empty_bar = bars + STAGES;           // [STAGES]
   uint64_t* tfull_bar = bars + 2 * STAGES;       // [2]
@@ -1014,7 +1115,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (!ptx::mbar_wait_bounded(&tfull_bar[acc], acc_ph, bail)) break;
       ptx::tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
-      epilogue_tile<EPI, COMM, 2>(a, pm, taddr, mb, nb, q, lane, stage, stage_it, a.C);
+      epilogue_tile<EPI, COMM, 2>(a, pm, taddr, mb, nb, q, lane, stage, stage_it, a.C,
+                                  a.epi_tma ? &pm.m[kMaxPeers] : nullptr, mb * BM + q * 32);
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&tempty_bar[acc]);
@@ -1025,6 +1127,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
     }
     if (COMM == kCommReduceScatter && tcount > 0) publish_tile<0>(a, prev_mb, lane, &warps_done[(tcount - 1) & 3]);
+    if (COMM != kCommReduceScatter && a.epi_tma && lane == 0) ptx::tma_store_wait<0>();  // staging buffers stay valid until read
   }
 
   ptx::tc_fence_before();
@@ -1076,6 +1179,15 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     return;
   }
   const int cta_id = static_cast<int>(blockIdx.x) - a.comm_ctas;
+  if ((COMM == kCommReduceScatter || COMM == kCommReduceScatterCe) && cta_id >= a.gemm_ctas) {
+    // reducer CTA (both CTAs of such a cluster, independently): sums the staged copies of this
+    // rank's row blocks as they complete, from the start of the launch
+    volatile uint32_t* rbail = reinterpret_cast<volatile uint32_t*>(bars + 28);
+    if (threadIdx.x == 0) *rbail = 0;
+    __syncthreads();
+    reduce_scatter_tail(a, smem, bars + 24, rbail, cta_id, a.gemm_ctas, COMM == kCommReduceScatterCe);
+    return;
+  }
   uint64_t* full_bar = bars;                           // [STAGES]  used in the leader
   uint64_t* empty_bar = bars + ST;           // [STAGES]  one per CTA
   uint64_t* tfull_bar = bars + 2 * ST;       // [2]       one per CTA
@@ -1235,14 +1347,19 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         if (owner == me)
           cb = reinterpret_cast<__nv_bfloat16*>(const_cast<char*>(a.comm.stage_local) +
                                                 static_cast<size_t>(me) * rpr * a.N * 2) - static_cast<size_t>(me) * rpr * a.ldc;
-        epilogue_tile<EPI, kCommNone, NBUF>(a, pm, taddr, mb, nb, q, lane, stage, stage_it, cb);
+        // through TMA: the own rows go through the map of this rank's staging buffer (slot [me] holds
+        // them at their global row index), the others through the map of the send buffer
+        const CUtensorMap* cm = a.epi_tma ? (owner == me ? &pm.m[0] : &pm.m[kMaxPeers]) : nullptr;
+        epilogue_tile<EPI, kCommNone, NBUF>(a, pm, taddr, mb, nb, q, lane, stage, stage_it, cb, cm, mb * BM + q * 32);
       } else {
-        epilogue_tile<EPI, COMM, NBUF>(a, pm, taddr, mb, nb, q, lane, stage, stage_it, a.C);
+        epilogue_tile<EPI, COMM, NBUF>(a, pm, taddr, mb, nb, q, lane, stage, stage_it, a.C,
+                                       a.epi_tma ? &pm.m[kMaxPeers] : nullptr, mb * BM + q * 32);
       }
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive_cluster(tempty0 + acc * 8);
       if (COMM == kCommReduceScatterCe && lane == 0) {
+        if (a.epi_tma) ptx::tma_store_wait<0>();  // the tile's TMA stores have landed
         // this warp's rows of the tile are written: count them for the chunk (or own row block)
         const int rpr = a.comm.rows_per_rank, me = a.comm.rank, n = a.comm.nranks, bpr = a.m_bpr;
         const int owner = min((mb * BM) / rpr, n - 1);
@@ -1266,6 +1383,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       }
     }
     if (COMM == kCommReduceScatter && tcount > 0) publish_tile<0>(a, prev_mb, lane, &warps_done[(tcount - 1) & 3]);
+    if (COMM != kCommReduceScatter && a.epi_tma && lane == 0) ptx::tma_store_wait<0>();  // staging buffers stay valid until read
   }
 
   ptx::tc_fence_before();

@@ -49,6 +49,10 @@ struct GemmFusion {
   uint32_t* done_peer[UCCL_MAX_LOCAL_RANKS] = {};
   void* rs_out = nullptr;
   int rs_ldo = 0;
+  // reduce-scatter: CTAs that do nothing but sum the staged copies while the others compute
+  // (0 = every CTA computes first and sums afterwards); tail_next: local word, zero at launch
+  int rs_reducers = 0;
+  uint32_t* tail_next = nullptr;
   // role 3 (reduce-scatter by copy engines): GemmLaunch.C is the local send buffer [M, N]; the
   // chunks of a slab are counted and flagged here, arrivals from the other ranks are flagged in ce_done
   uint32_t* slab_count = nullptr;

@@ -232,6 +232,7 @@ PYBIND11_MODULE(_uccl_bindings, m) {
   m.def("set_fused_rs_options", [](uintptr_t c, int rsMode, int ceChunks) {
     check(ucclCommSetFusedRsOptions(C(c), rsMode, ceChunks), "ucclCommSetFusedRsOptions");
   });
+  m.def("set_fused_rs_reducers", [](uintptr_t c, int n) { check(ucclCommSetFusedRsReducers(C(c), n), "ucclCommSetFusedRsReducers"); });
   m.def("set_fused_options", [](uintptr_t c, int agMode, int commCtas, int ceChunks) {
     check(ucclCommSetFusedOptions(C(c), agMode, commCtas, ceChunks), "ucclCommSetFusedOptions");
   });

@@ -307,6 +307,10 @@ ucclResult_t ucclCommSetFusedOptions(ucclComm_t comm, int agMode, int commCtas, 
  * chunk of a rank's rows to its owner (ceChunks chunks per rank, at most 8).  UCCL_FUSED_RS=kernel|ce
  * and UCCL_FUSED_RS_CHUNKS win. */
 ucclResult_t ucclCommSetFusedRsOptions(ucclComm_t comm, int rsMode, int ceChunks);
+/* CTAs of the fused GEMM -> reduce-scatter launch that do nothing but sum the staged partial tiles of
+ * this rank's rows while the others compute (0 = none: every CTA computes, then sums; at most 64).
+ * Worth it where the links rather than the tensor cores set the pace.  UCCL_FUSED_RS_REDUCERS wins. */
+ucclResult_t ucclCommSetFusedRsReducers(ucclComm_t comm, int reducerCtas);
 
 #ifdef __cplusplus
 }

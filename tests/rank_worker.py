@@ -443,8 +443,14 @@ def case_tp_mlp(comm, rank, n, args):
     modes = [("ce", "kernel"), ("kernel", "kernel"), ("spread", "kernel")] if n > 1 else [("ce", "kernel")]
     if n > 1:  # reduce-scatter carried by copy engines
         modes += [("spread", "ce"), ("ce", "ce")]
+    if args:  # a subset, "ag/rs,ag/rs,..." (for bisecting a failure)
+        modes = [tuple(m.split("/")) for m in args[0].split(",")]
+    if n > 1 and not args:
+        modes += [("ce", "kernel+reducers")]  # a few CTAs only sum while the others compute
     for ag_mode, rs_mode in modes:
         os.environ["UCCL_FUSED_AG"] = ag_mode
+        os.environ["UCCL_FUSED_RS_REDUCERS"] = "8" if rs_mode.endswith("+reducers") else "0"
+        rs_mode = rs_mode.split("+")[0]
         os.environ["UCCL_FUSED_RS"] = rs_mode
         shapes = [(512, 1024, 256 * n), (1024, 3584 * 2, 128 * n)]
         if rs_mode == "ce":
@@ -470,6 +476,7 @@ def case_tp_mlp(comm, rank, n, args):
                 fail.append((ag_mode, "x_full not gathered", hidden, tokens))
     os.environ.pop("UCCL_FUSED_AG", None)
     os.environ.pop("UCCL_FUSED_RS", None)
+    os.environ.pop("UCCL_FUSED_RS_REDUCERS", None)
     return {"fail": fail, "nvls": comm.info["nvls"], "async": comm.async_error(), "last": comm.last_error()}
 
 

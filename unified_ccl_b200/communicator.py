@@ -318,6 +318,10 @@ class Communicator:
         of a rank's rows to its owner, ``ce_chunks`` chunks per rank)."""
         _C.set_fused_rs_options(self._comm, {"auto": 0, "kernel": 1, "ce": 2}[rs_mode], int(ce_chunks))
 
+    def set_fused_rs_reducers(self, reducer_ctas: int = 0):
+        """CTAs of the fused GEMM -> reduce-scatter launch that only sum the staged partial tiles (0 = none)."""
+        _C.set_fused_rs_reducers(self._comm, int(reducer_ctas))
+
     def load_tuning(self, path: str):
         _C.load_tuning(self._comm, path)
 

@@ -98,7 +98,16 @@ class TensorParallelMLP:
         return {cands[i]: round(avg[i], 1) for i in range(len(cands))}
 
     # candidates of autotune_rs(): (reduce-scatter mode, copy-engine chunks per rank)
-    RS_CANDIDATES = (("kernel", 0), ("ce", 1), ("ce", 2), ("ce", 4), ("ce", 8))
+    # (mode, copy-engine chunks per rank | for "kernel": CTAs that only sum)
+    RS_CANDIDATES = (("kernel", 0), ("kernel", 8), ("kernel", 16), ("kernel", 24), ("ce", 1), ("ce", 2))
+
+    def _apply_rs(self, mode, arg):
+        if mode == "kernel":
+            self.comm.set_fused_rs_options("kernel", 0)
+            self.comm.set_fused_rs_reducers(arg)
+        else:
+            self.comm.set_fused_rs_options(mode, arg)
+            self.comm.set_fused_rs_reducers(0)
 
     def autotune_rs(self, iters: int = 3, candidates=None):
         """The same for the GEMM -> reduce-scatter half (``self.h`` must hold activations, e.g. after one
@@ -110,7 +119,7 @@ class TensorParallelMLP:
         stream = torch.cuda.current_stream(self.h.device)
         for i, (mode, chunks) in enumerate(cands):
             try:
-                self.comm.set_fused_rs_options(mode, chunks)
+                self._apply_rs(mode, chunks)
                 gemm_reduce_scatter(self.comm, self.h, self.w_down, self.c_partial, out=self.y)  # warm-up
                 s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 s.record(stream)
@@ -125,7 +134,7 @@ class TensorParallelMLP:
         stream.synchronize()
         avg = (times / self.tp).tolist()
         best = min(range(len(cands)), key=lambda i: avg[i])
-        self.comm.set_fused_rs_options(*cands[best])
+        self._apply_rs(*cands[best])
         self.rs_choice = cands[best]
         return {cands[i]: round(avg[i], 1) for i in range(len(cands))}
 
