@@ -100,7 +100,7 @@ def main():
                 os.environ["UCCL_NORM_DEBUG"] = str(bits)
                 parts[name] = round(timed(lambda: allreduce_residual_rmsnorm(comm, x, res, gamma, 1e-6, out=out, residual_out=res)), 1)
             os.environ["UCCL_NORM_DEBUG"] = "0"
-            for rows in (1, 2, 4):  # rows per pass of phase A on the switch path
+            for rows in (0, 1, 2, 4):  # switch path: 0 = own rows normalised from registers; else rows per pass of the all-reduce phase
                 os.environ["UCCL_NORM_MC_ROWS"] = str(rows)
                 parts["mc_rows_%d" % rows] = round(timed(lambda: allreduce_residual_rmsnorm(comm, x, res, gamma, 1e-6, out=out, residual_out=res)), 1)
             os.environ.pop("UCCL_NORM_MC_ROWS", None)

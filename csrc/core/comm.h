@@ -55,6 +55,8 @@ struct ProxyState {
   std::atomic<uint64_t> completions{0};
 };
 
+constexpr int kCeChunkEvents = 64;
+
 struct TraceEvent {
   const char* name;
   size_t bytes;
@@ -99,6 +101,7 @@ struct Comm {
   cudaStream_t ceStream[UCCL_MAX_LOCAL_RANKS] = {};
   cudaEvent_t ceEvent[UCCL_MAX_LOCAL_RANKS] = {};
   cudaEvent_t ceStart = nullptr;
+  cudaEvent_t ceChunkEvent[64] = {};  // copy-engine all-gather with a flag stream: one per pushed chunk
   bool ceReady = false;
   // reduce-scatter by copy engines: local send buffer (grown on demand) and chunk counters / flags
   void* rsSendBuf = nullptr;

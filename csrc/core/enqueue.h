@@ -46,8 +46,8 @@ ucclResult_t sideCopyBegin(Comm* c, void* dst, const void* src, size_t bytes, cu
 ucclResult_t sideCopyEnd(Comm* c, cudaStream_t s);
 // copy-engine all-gather with per-row-block arrival flags (all-gather -> GEMM fusion)
 ucclResult_t allGatherPushBegin(Comm* c, const void* shard, char* const* fullPeer, char* const* readyPeer,
-                                size_t shardBytes, int blocksPerRank, bool copyOwn, int lanes, cudaStream_t s);
-ucclResult_t allGatherPushEnd(Comm* c, bool copyOwn, int lanes, cudaStream_t s);
+                                size_t shardBytes, int blocksPerRank, bool copyOwn, int lanes, bool flagStream, cudaStream_t s);
+ucclResult_t allGatherPushEnd(Comm* c, bool copyOwn, int lanes, bool flagStream, cudaStream_t s);
 // copy-engine transport of the GEMM -> reduce-scatter fusion (see enqueue_ring_ce.cc)
 ucclResult_t reduceScatterPushPrepare(Comm* c, cudaStream_t s);
 ucclResult_t reduceScatterPushCopies(Comm* c, const char* sendBuf, char* const* stagePeer, char* const* ceDonePeer,

@@ -116,7 +116,7 @@ int cePushStreams(Comm* c, int lanes, bool copyOwn, cudaStream_t* out) {
 }  // namespace
 
 ucclResult_t allGatherPushBegin(Comm* c, const void* shard, char* const* fullPeer, char* const* readyPeer,
-                                size_t shardBytes, int blocksPerRank, bool copyOwn, int lanes, cudaStream_t s) {
+                                size_t shardBytes, int blocksPerRank, bool copyOwn, int lanes, bool flagStream, cudaStream_t s) {
   const ucclResult_t r = ensureCeStreams(c);
   if (r != ucclSuccess) return r;
   const int n = c->localRanks, me = c->localRank;
@@ -136,6 +136,19 @@ ucclResult_t allGatherPushBegin(Comm* c, const void* shard, char* const* fullPee
   const char* src = static_cast<const char*>(shard);
   const size_t rowOff = static_cast<size_t>(me) * shardBytes;
   const int usedLanes = lanes > 0 ? std::min(lanes, n - 1) : 0;
+  // With lanes the data copies of a lane run back to back; each arrival flag is one more small copy
+  // in the same stream and costs a gap of its own.  flagStream moves the flag copies to a stream of
+  // their own (the last one, which no lane uses when n > lanes + 2), each behind an event recorded
+  // after its data copy, so the data stream never stops for a flag.
+  flagStream = flagStream && usedLanes > 0 && n - 1 > usedLanes + (copyOwn ? 1 : 0);
+  cudaStream_t fs = flagStream ? c->ceStream[n - 1] : nullptr;
+  if (flagStream) {
+    if (cudaStreamWaitEvent(fs, c->ceStart, 0) != cudaSuccess) return cudaFail(c, "cudaStreamWaitEvent");
+    for (int i = 0; i < kCeChunkEvents; ++i)
+      if (!c->ceChunkEvent[i] && cudaEventCreateWithFlags(&c->ceChunkEvent[i], cudaEventDisableTiming) != cudaSuccess)
+        return cudaFail(c, "cudaEventCreate");
+  }
+  int nextEvent = 0;
   auto pushChunk = [&](int p, int j, cudaStream_t st) -> ucclResult_t {
     const int b0 = static_cast<int>(static_cast<long long>(blocksPerRank) * j / chunks);
     const int b1 = static_cast<int>(static_cast<long long>(blocksPerRank) * (j + 1) / chunks);
@@ -143,8 +156,14 @@ ucclResult_t allGatherPushBegin(Comm* c, const void* shard, char* const* fullPee
     const size_t off = b0 * blkBytes, len = (b1 - b0) * blkBytes;
     if (cudaMemcpyAsync(fullPeer[p] + rowOff + off, src + off, len, cudaMemcpyDeviceToDevice, st) != cudaSuccess)
       return cudaFail(c, "cudaMemcpyAsync");
+    cudaStream_t flagSt = st;
+    if (flagStream && nextEvent < kCeChunkEvents) {
+      cudaEvent_t ev = c->ceChunkEvent[nextEvent++];
+      if (cudaEventRecord(ev, st) != cudaSuccess || cudaStreamWaitEvent(fs, ev, 0) != cudaSuccess) return cudaFail(c, "cudaEventRecord");
+      flagSt = fs;
+    }
     if (cudaMemcpyAsync(readyPeer[p] + (static_cast<size_t>(me) * blocksPerRank + b0) * kGemmFlagStrideBytes, c->onesDev,
-                        static_cast<size_t>(b1 - b0) * kGemmFlagStrideBytes, cudaMemcpyDeviceToDevice, st) != cudaSuccess)
+                        static_cast<size_t>(b1 - b0) * kGemmFlagStrideBytes, cudaMemcpyDeviceToDevice, flagSt) != cudaSuccess)
       return cudaFail(c, "cudaMemcpyAsync");
     return ucclSuccess;
   };
@@ -169,9 +188,15 @@ ucclResult_t allGatherPushBegin(Comm* c, const void* shard, char* const* fullPee
     return cudaFail(c, "cudaMemcpyAsync");
   return ucclSuccess;
 }
-ucclResult_t allGatherPushEnd(Comm* c, bool copyOwn, int lanes, cudaStream_t s) {
+ucclResult_t allGatherPushEnd(Comm* c, bool copyOwn, int lanes, bool flagStream, cudaStream_t s) {
   cudaStream_t streams[UCCL_MAX_LOCAL_RANKS + 1];
   const int nstreams = cePushStreams(c, lanes, copyOwn, streams);
+  const int n = c->localRanks;
+  const int usedLanes = lanes > 0 ? std::min(lanes, n - 1) : 0;
+  if (flagStream && usedLanes > 0 && n - 1 > usedLanes + (copyOwn ? 1 : 0)) {
+    if (cudaEventRecord(c->ceEvent[n - 1], c->ceStream[n - 1]) != cudaSuccess) return cudaFail(c, "cudaEventRecord");
+    if (cudaStreamWaitEvent(s, c->ceEvent[n - 1], 0) != cudaSuccess) return cudaFail(c, "cudaStreamWaitEvent");
+  }
   for (int i = 0; i < nstreams; ++i) {
     // one event per stream: the events array has an entry for every local rank
     if (cudaEventRecord(c->ceEvent[i], streams[i]) != cudaSuccess) return cudaFail(c, "cudaEventRecord");

@@ -160,8 +160,9 @@ extern "C" ucclResult_t ucclAllReduceResidualRMSNorm(const void* x, const void* 
     a.debug = dbg ? atoi(dbg) : 0;
   }
 #endif
-  a.mcRows = 1;
+  a.mcRows = 4;  // rows per pass of the all-reduce phase on the switch path; 0 = normalise own rows from registers
   if (const char* e = getenv("UCCL_NORM_MC_ROWS")) a.mcRows = atoi(e);
+  if (a.mcRows < 0 || a.mcRows > 4) a.mcRows = 4;
   commCount(c, ucclCollAllReduce, bytes, c->arena && c->arena->mc ? ucclAlgoNvls : ucclAlgoTwoShot);
   if (c->nRanks == 1) {
     a.dc.nranks = 1;
@@ -296,12 +297,16 @@ extern "C" ucclResult_t ucclAllGatherGemm(const void* xShard, void* xFull, const
     // 530 us with two, 559 us with a stream per peer)
     int lanes = c->fusedAgMode == 0 ? (n > 2 ? 1 : 0) : c->fusedCommCtas;
     if (const char* e = getenv("UCCL_FUSED_CE_LANES")) lanes = atoi(e);
+    // 32 + k lanes: k lanes, and the arrival flags travel on a stream of their own
+    bool flagStream = lanes >= 32;
+    if (flagStream) lanes -= 32;
+    if (const char* e = getenv("UCCL_FUSED_CE_FLAG_STREAM")) flagStream = atoi(e) != 0;
     if (lanes < 0 || n <= 2) lanes = 0;
     f.a_peer_major = lanes > 0 ? 1 : 0;
-    if ((r = allGatherPushBegin(c, xShard, fullPeer, readyPeer, shardBytes, rows / 128, !f.a_inplace, lanes, s)) != ucclSuccess)
+    if ((r = allGatherPushBegin(c, xShard, fullPeer, readyPeer, shardBytes, rows / 128, !f.a_inplace, lanes, flagStream, s)) != ucclSuccess)
       return r;
     if ((r = launchGemmBf16(g, &f, s)) != ucclSuccess) return r;
-    return allGatherPushEnd(c, !f.a_inplace, lanes, s);
+    return allGatherPushEnd(c, !f.a_inplace, lanes, flagStream, s);
   }
   commCount(c, ucclCollAllGather, static_cast<size_t>(M) * K * 2, ucclAlgoOneShot);
   f.a_spread = agMode == 3 ? 1 : 0;

@@ -406,6 +406,8 @@ void destroyComm(Comm* c) {
       if (c->ceEvent[i]) cudaEventDestroy(c->ceEvent[i]);
     }
     if (c->ceStart) cudaEventDestroy(c->ceStart);
+    for (cudaEvent_t e : c->ceChunkEvent)
+      if (e) cudaEventDestroy(e);
     if (c->onesDev) cudaFree(c->onesDev);
     if (c->rsSendBuf) cudaFree(c->rsSendBuf);
     if (c->rsCtl) cudaFree(c->rsCtl);

@@ -119,7 +119,7 @@ struct ArNormArgs {
   char* resOutUser;                      // set when `resOut` is the staging area: copy there last
   int tokens, hidden;
   float eps;
-  int mcRows;  // rows per pass of phase A on the switch path (1, 2 or 4)
+  int mcRows;  // switch path: rows per pass of the all-reduce phase (1, 2 or 4), own rows normalised in phase B; 0 = from registers, one row per pass
   int debug;  // experiment switches (UCCL_NORM_DEBUG): 1 no phase B, 2 no phase-A stores, 4 no phase A
 };
 cudaError_t launchArNormKernel(const ArNormArgs& a, int blocks, cudaStream_t stream);

@@ -151,7 +151,13 @@ __global__ void __launch_bounds__(kThreads, 1) ar_norm_kernel(const __grid_const
   // enough to cover the latency (the links, not the loads in flight, are the limit) and lets the
   // stores of one pass travel while the loads of the next are already out; the peer path takes R.
   const NormPass npB = np;
-  if (a.inMc) np.R = max(1, min(np.R, a.mcRows));
+  // Through the switch phase A is a plain all-reduce loop over this rank's rows (reduce in the
+  // switch, add the residual, broadcast through the switch), as many rows in flight as the
+  // registers hold and no CTA-wide reduction in between; the rows are normalised in phase B with
+  // everybody else's, from local memory.  mcRows = 1, 2 or 4 rows per pass, 0 = the older form
+  // that normalises its own rows from registers one row per pass.
+  const bool splitNorm = a.inMc && a.resOutMc && a.mcRows > 0;
+  if (a.inMc) np.R = splitNorm ? max(1, min(np.R, a.mcRows)) : 1;
   for (size_t r0 = b; r0 < (UCCL_NORM_DBG(a, 4) ? 0 : myLen); r0 += static_cast<size_t>(B) * np.R) {
     size_t rowIdx[kNormMaxRows];
     int rowsHere = 0;
@@ -203,11 +209,11 @@ __global__ void __launch_bounds__(kThreads, 1) ar_norm_kernel(const __grid_const
         }
       }
     }
-    normalise_rows(np, h, rowsHere, rowIdx, a.gamma, a.outLocal, rowBytes, a.eps, a.hidden);
+    if (!splitNorm) normalise_rows(np, h, rowsHere, rowIdx, a.gamma, a.outLocal, rowBytes, a.eps, a.hidden);
   }
   if (!rank_barrier(dc)) return;
   // ---- phase B: rows owned by the other ranks, now present in my copy of the residual stream
-  for (int q = 1; q < (UCCL_NORM_DBG(a, 1) ? 0 : n); ++q) {
+  for (int q = splitNorm ? 0 : 1; q < (UCCL_NORM_DBG(a, 1) ? 0 : n); ++q) {
     const int p = (me + q) % n;
     size_t ro, rl;
     split(static_cast<size_t>(a.tokens), n, p, &ro, &rl);

@@ -301,6 +301,7 @@ ucclResult_t ucclCommSetBlocks(ucclComm_t comm, int blocks);
  * per peer, k = k streams that serve the peers one after the other, nearest first).
  * ceChunks: copies per peer (mode 1).
  * The environment variables UCCL_FUSED_AG / UCCL_FUSED_COMM_CTAS / UCCL_FUSED_CE_CHUNKS win. */
+/* With agMode 1, commCtas = 32 + k selects k lanes plus a separate stream for the arrival flags. */
 ucclResult_t ucclCommSetFusedOptions(ucclComm_t comm, int agMode, int commCtas, int ceChunks);
 /* Options of the fused GEMM -> reduce-scatter; 0 keeps a default.  rsMode: 1 = the epilogue TMA-stores
  * every tile into the owner's memory, 2 = tiles stay local and copy engines carry each finished

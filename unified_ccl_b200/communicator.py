@@ -308,7 +308,8 @@ class Communicator:
     def set_fused_options(self, ag_mode: str = "auto", comm_ctas: int = 0, ce_chunks: int = 0):
         """How the all-gather -> GEMM fusion moves its rows: ``"ce"`` (copy engines, ``ce_chunks`` copies per
         peer; ``comm_ctas`` then is the number of copy-engine lanes, 0 = one stream per peer, k = k streams
-        that serve the peers one after the other), ``"kernel"`` (``comm_ctas`` communication CTAs inside the
+        that serve the peers one after the other, 32 + k = k streams plus one more stream that carries the
+        arrival flags so that the data copies run back to back), ``"kernel"`` (``comm_ctas`` communication CTAs inside the
         GEMM launch) or ``"spread"`` (a forwarder warp in every GEMM CTA); 0 keeps a default."""
         _C.set_fused_options(self._comm, {"auto": 0, "ce": 1, "kernel": 2, "spread": 3}[ag_mode], int(comm_ctas), int(ce_chunks))
 

@@ -50,7 +50,8 @@ class TensorParallelMLP:
     # candidates of autotune(): (all-gather mode, communication CTAs or copy-engine lanes, chunks per peer)
     # "spread" stores through the switch where the buffer has a multicast alias and there are more than two
     # ranks; "spread_uc" is the same forwarder warp with unicast bulk copies
-    AG_CANDIDATES = (("ce", 0, 1), ("ce", 0, 2), ("ce", 0, 4), ("ce", 1, 2), ("ce", 2, 2), ("ce", 1, 4),
+    # "ce" with 32 + k communication CTAs: k copy-engine lanes and a stream of its own for the arrival flags
+    AG_CANDIDATES = (("ce", 0, 2), ("ce", 1, 2), ("ce", 1, 4), ("ce", 33, 1), ("ce", 33, 2), ("ce", 33, 4), ("ce", 34, 2),
                      ("spread", 0, 0), ("spread_uc", 0, 0), ("kernel", 4, 0), ("kernel", 8, 0), ("kernel", 16, 0))
 
     def _apply_ag(self, mode, ctas, chunks):
