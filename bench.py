@@ -21,6 +21,10 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
+# read by CUDA when the context is created: enough hardware queues for the side streams of the
+# copy-engine transports (the package sets the same default on import; both arms run under it)
+os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "32")
+
 BATCH, SEQ, HIDDEN, FFN = 4, 4096, 4096, 14336
 
 
@@ -81,10 +85,10 @@ def main():
     if world > 1 and not os.environ.get("UCCL_FUSED_AG"):
         autotune = {"%s/ctas%d/chunks%d" % k: v for k, v in mlp.autotune(x_dev).items()}
         autotune["chosen"] = "%s/ctas%d/chunks%d" % mlp.ag_choice
-    # untimed: the same for the GEMM -> reduce-scatter half (epilogue stores or copy engines)
-    if world > 1 and not os.environ.get("UCCL_FUSED_RS"):
+    # untimed: the same for the GEMM -> reduce-scatter half (how many CTAs only sum)
+    if world > 1 and not os.environ.get("UCCL_FUSED_RS_REDUCERS"):
         mlp(x_dev)  # fills the activations the second half works on
-        autotune_rs = {"%s/%d" % k: v for k, v in mlp.autotune_rs().items()}  # kernel/<reducer CTAs> or ce/<chunks>
+        autotune_rs = {"%s/%d" % k: v for k, v in mlp.autotune_rs().items()}  # kernel/<reducer CTAs>
         autotune_rs["chosen"] = "%s/%d" % mlp.rs_choice
 
     def barrier():
@@ -192,7 +196,8 @@ def main():
             "data": "synthetic activations N(0,1) seeded per rank, random-init weights N(0,0.02)",
             "config": {"model": "llama-style SwiGLU MLP block", "global_batch": BATCH, "seq_len": SEQ, "hidden": HIDDEN,
                        "ffn": FFN, "parallelism": "tp%d" % world,
-                       "l2": "per-rank working set (weights + activations + scratch) exceeds the 126 MB L2; no flush"},
+                       "l2": "per-rank working set (weights + activations + scratch) exceeds the 126 MB L2; no flush",
+                       "cuda_device_max_connections": os.environ.get("CUDA_DEVICE_MAX_CONNECTIONS")},
             "nccl_cublas_us": round(ms_base * 1e3, 2),
             "speedup_vs_nccl_cublas": round(ms_base / ms_ours, 3),
             "nccl_cublas_fused_swiglu_us": round(ms_base_fused * 1e3, 2),

@@ -184,7 +184,9 @@ def main():
                     dst = torch.empty(cnt * n, dtype=dt, device=dev)
                     src = torch.ones(cnt * n, dtype=dt, device=dev)
                     record(coll, "nccl", "nccl", "-", dtn, nbytes, timed(lambda: dist.all_to_all_single(dst, src), it), (n - 1) / n, False)
-                    record(coll, "uccl", "two_shot", "simple", dtn, nbytes, timed(lambda: comm.alltoall(sym, dst), it), (n - 1) / n, True)
+                    uccl_algo(coll, "alltoall", "two_shot", "simple", dtn, nbytes, lambda: comm.alltoall(sym, dst), it, (n - 1) / n)
+                    comm.set_algo("auto", "auto")
+                    record(coll, "uccl", "auto", "auto", dtn, nbytes, timed(lambda: comm.alltoall(sym, dst), it), (n - 1) / n, True)
                     comm.free(sym)
                 elif coll == "sendrecv":
                     cnt = nbytes // es

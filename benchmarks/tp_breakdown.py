@@ -127,17 +127,10 @@ def main():
         os.environ["UCCL_FUSED_DEBUG"] = str(bits)
         res[name] = timed(rs)
     os.environ["UCCL_FUSED_DEBUG"] = "0"
-    if args.rs_ce:
-        for chunks in (1, 2, 4, 8):
-            comm.set_fused_rs_options("ce", chunks)
-            res["rs_ce_chunks%d" % chunks] = timed(rs)
-        rs()
-        torch.cuda.synchronize()
-        y2 = y.clone()
-        nccl_down()
-        torch.cuda.synchronize()
-        res["rs_ce_max_abs_err"] = float((y2.float() - y.float()).abs().max())
-        comm.set_fused_rs_options()
+    for red in (8, 16):
+        comm.set_fused_rs_reducers(red)
+        res["rs_tma_reducers%d" % red] = timed(rs)
+    comm.set_fused_rs_reducers(0)
     res["async_error"] = comm.async_error()
     if rank == 0:
         print(json.dumps(res), flush=True)

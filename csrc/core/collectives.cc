@@ -2,6 +2,9 @@
 // the current group.  The validation matrix follows the reference's front door
 // (src/collectives.cc:29-125): invalid / aborted communicator, count == 0 succeeds without
 // touching the buffers, null buffers, data type and reduction operator ranges.
+#include <algorithm>
+#include <vector>
+
 #include "enqueue.h"
 #include "log.h"
 
@@ -183,6 +186,69 @@ extern "C" ucclResult_t ucclCommQueryTuning(ucclComm_t comm, ucclCollKind_t coll
   return ucclSuccess;
 }
 
+// Canaries (UCCL_CANARY=1).  A buffer from ucclMemAlloc then sits between two painted regions of
+// its own mapping: kCanaryBytes in front, and everything from its end to the end of the mapping
+// (at least kCanaryBytes, checked up to kCanaryTailMax) behind.  A store that misses the buffer by
+// a little -- this rank's or a peer's, through the peer or the multicast alias -- lands there
+// instead of in a neighbour, and ucclMemCheck / ucclMemFree find it.  Stores that miss by more than
+// the mapping reach unmapped addresses, which the hardware reports.
+static constexpr size_t kCanaryBytes = 4096;
+static constexpr size_t kCanaryTailMax = 64u << 10;
+static constexpr unsigned char kCanaryByte = 0xC5;
+
+static size_t canaryTail(const SymSegment* seg) {
+  return std::min(kCanaryTailMax, seg->mapSize - seg->guard - seg->userSize);
+}
+
+static void paintCanaries(SymSegment* seg) {
+  cudaMemset(seg->local, kCanaryByte, seg->guard);
+  cudaMemset(seg->local + seg->guard + seg->userSize, kCanaryByte, canaryTail(seg));
+  cudaDeviceSynchronize();
+}
+
+// Offset (relative to the caller's pointer; negative = in front) of the first overwritten canary
+// byte of `seg`, or false when both canaries are intact.
+static bool canaryBroken(const SymSegment* seg, long long* where) {
+  if (!seg->guard) return false;
+  const size_t tail = canaryTail(seg);
+  std::vector<unsigned char> h(seg->guard + tail);
+  if (cudaMemcpy(h.data(), seg->local, seg->guard, cudaMemcpyDeviceToHost) != cudaSuccess ||
+      cudaMemcpy(h.data() + seg->guard, seg->local + seg->guard + seg->userSize, tail, cudaMemcpyDeviceToHost) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return false;
+  }
+  for (size_t i = 0; i < h.size(); ++i)
+    if (h[i] != kCanaryByte) {
+      *where = i < seg->guard ? static_cast<long long>(i) - static_cast<long long>(seg->guard)
+                              : static_cast<long long>(seg->userSize + (i - seg->guard));
+      return true;
+    }
+  return false;
+}
+
+extern "C" ucclResult_t ucclMemCheck(ucclComm_t comm) {
+  Comm* c = toComm(comm);
+  if (!commValid(c)) return ucclInvalidArgument;
+  if (!c->p2pReady || !c->cfg.canary) return ucclSuccess;
+  int prev = -1;
+  cudaGetDevice(&prev);
+  if (prev != c->cudaDev) cudaSetDevice(c->cudaDev);
+  cudaDeviceSynchronize();
+  c->bootstrap.barrier();  // every rank's stores into my buffers have landed
+  ucclResult_t r = ucclSuccess;
+  for (SymSegment* seg : c->heap.segments()) {
+    long long where = 0;
+    if (canaryBroken(seg, &where)) {
+      commSetError(c, "memory check: buffer %p (%zu bytes) has a store outside its bounds at byte offset %lld",
+                   static_cast<void*>(seg->local + seg->guard), seg->userSize, where);
+      r = ucclInternalError;
+      break;
+    }
+  }
+  if (prev != c->cudaDev && prev >= 0) cudaSetDevice(prev);
+  return r;
+}
+
 extern "C" ucclResult_t ucclMemAlloc(void** ptr, size_t size, ucclComm_t comm) {
   Comm* c = toComm(comm);
   if (!commValid(c) || !ptr || size == 0) return ucclInvalidArgument;
@@ -202,10 +268,16 @@ extern "C" ucclResult_t ucclMemAlloc(void** ptr, size_t size, ucclComm_t comm) {
   cudaGetDevice(&prev);
   if (prev != c->cudaDev) cudaSetDevice(c->cudaDev);
   SymSegment* seg = nullptr;
-  ucclResult_t r = c->heap.alloc(size, &seg);
+  const size_t guard = c->cfg.canary ? kCanaryBytes : 0;
+  ucclResult_t r = c->heap.alloc(size + 2 * guard, &seg);
+  if (r == ucclSuccess) {
+    seg->guard = guard;
+    seg->userSize = size;
+    if (guard) paintCanaries(seg);
+  }
   if (prev != c->cudaDev && prev >= 0) cudaSetDevice(prev);
   if (r != ucclSuccess) return r;
-  *ptr = seg->local;
+  *ptr = seg->local + guard;
   return ucclSuccess;
 }
 
@@ -218,15 +290,20 @@ extern "C" ucclResult_t ucclMemFree(void* ptr, ucclComm_t comm) {
     return ucclSuccess;
   }
   SymSegment* seg = c->heap.find(ptr, 1);
-  if (!seg || seg->local != ptr || seg == c->arena) return ucclInvalidArgument;
+  if (!seg || seg->local + seg->guard != ptr || seg == c->arena) return ucclInvalidArgument;
   int prev = -1;
   cudaGetDevice(&prev);
   if (prev != c->cudaDev) cudaSetDevice(c->cudaDev);
   cudaDeviceSynchronize();
   c->bootstrap.barrier();  // peers may still be reading this memory
+  long long where = 0;
+  const bool broken = canaryBroken(seg, &where);
+  if (broken)
+    commSetError(c, "memory check: buffer %p (%zu bytes) was freed with a store outside its bounds at byte offset %lld",
+                 ptr, seg->userSize, where);
   ucclResult_t r = c->heap.release(seg);
   if (prev != c->cudaDev && prev >= 0) cudaSetDevice(prev);
-  return r;
+  return broken && r == ucclSuccess ? ucclInternalError : r;
 }
 
 extern "C" ucclResult_t ucclMemPeerPointer(const void* ptr, int peer, ucclComm_t comm, void** peerPtr) {

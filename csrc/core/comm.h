@@ -55,8 +55,6 @@ struct ProxyState {
   std::atomic<uint64_t> completions{0};
 };
 
-constexpr int kCeChunkEvents = 64;
-
 struct TraceEvent {
   const char* name;
   size_t bytes;
@@ -101,13 +99,7 @@ struct Comm {
   cudaStream_t ceStream[UCCL_MAX_LOCAL_RANKS] = {};
   cudaEvent_t ceEvent[UCCL_MAX_LOCAL_RANKS] = {};
   cudaEvent_t ceStart = nullptr;
-  cudaEvent_t ceChunkEvent[64] = {};  // copy-engine all-gather with a flag stream: one per pushed chunk
   bool ceReady = false;
-  // reduce-scatter by copy engines: local send buffer (grown on demand) and chunk counters / flags
-  void* rsSendBuf = nullptr;
-  size_t rsSendBytes = 0;
-  void* rsCtl = nullptr;              // u32 counts at +0, u64 flags at +1024
-  int fusedRsMode = 0, fusedRsChunks = 0;  // ucclCommSetFusedRsOptions (0 = default)
   int fusedRsReducers = 0;                  // ucclCommSetFusedRsReducers: CTAs that only sum
   void* onesDev = nullptr;            // 32-bit ones at the GEMM flag stride (source of copy-engine flag writes)
 

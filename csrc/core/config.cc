@@ -122,6 +122,7 @@ Config loadConfig() {
   if (c.netChunkBytes < 4096) c.netChunkBytes = 4096;
   c.jitterUs = (int)envLong("UCCL_JITTER_US", 0);
   if (c.jitterUs < 0) c.jitterUs = 0;
+  c.canary = envLong("UCCL_CANARY", 0) != 0;
   c.fusedCeChunks = (int)envLong("UCCL_FUSED_CE_CHUNKS", 0);
   if (c.fusedCeChunks < 0) c.fusedCeChunks = 0;
   return c;

@@ -36,6 +36,7 @@ struct Config {
   std::string traceFile;                 // UCCL_TRACE_FILE
   size_t netChunkBytes = 512u << 10;     // UCCL_NET_CHUNK_BYTES (bounce slot size)
   int jitterUs = 0;                      // UCCL_JITTER_US: random host-side pauses of up to this many microseconds (testing)
+  bool canary = false;                   // UCCL_CANARY=1: guard words around every ucclMemAlloc buffer, verified by ucclMemCheck / ucclMemFree
   int fusedCeChunks = 0;                 // UCCL_FUSED_CE_CHUNKS: copies per peer of the copy-engine all-gather
 };
 

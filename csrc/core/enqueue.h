@@ -46,13 +46,8 @@ ucclResult_t sideCopyBegin(Comm* c, void* dst, const void* src, size_t bytes, cu
 ucclResult_t sideCopyEnd(Comm* c, cudaStream_t s);
 // copy-engine all-gather with per-row-block arrival flags (all-gather -> GEMM fusion)
 ucclResult_t allGatherPushBegin(Comm* c, const void* shard, char* const* fullPeer, char* const* readyPeer,
-                                size_t shardBytes, int blocksPerRank, bool copyOwn, int lanes, bool flagStream, cudaStream_t s);
-ucclResult_t allGatherPushEnd(Comm* c, bool copyOwn, int lanes, bool flagStream, cudaStream_t s);
-// copy-engine transport of the GEMM -> reduce-scatter fusion (see enqueue_ring_ce.cc)
-ucclResult_t reduceScatterPushPrepare(Comm* c, cudaStream_t s);
-ucclResult_t reduceScatterPushCopies(Comm* c, const char* sendBuf, char* const* stagePeer, char* const* ceDonePeer,
-                                     unsigned long long* slabFlag, size_t slabBytes, int chunks);
-ucclResult_t reduceScatterPushEnd(Comm* c, unsigned long long* slabFlag, int nflags, cudaStream_t s);
+                                size_t shardBytes, int blocksPerRank, bool copyOwn, int lanes, cudaStream_t s);
+ucclResult_t allGatherPushEnd(Comm* c, bool copyOwn, int lanes, cudaStream_t s);
 ucclResult_t enqueueNetGpu(Comm* c, const CollOp& op);
 ucclResult_t enqueueNetGpuP2p(Comm* c, const std::vector<CollOp>& ops);
 

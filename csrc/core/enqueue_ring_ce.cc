@@ -116,7 +116,7 @@ int cePushStreams(Comm* c, int lanes, bool copyOwn, cudaStream_t* out) {
 }  // namespace
 
 ucclResult_t allGatherPushBegin(Comm* c, const void* shard, char* const* fullPeer, char* const* readyPeer,
-                                size_t shardBytes, int blocksPerRank, bool copyOwn, int lanes, bool flagStream, cudaStream_t s) {
+                                size_t shardBytes, int blocksPerRank, bool copyOwn, int lanes, cudaStream_t s) {
   const ucclResult_t r = ensureCeStreams(c);
   if (r != ucclSuccess) return r;
   const int n = c->localRanks, me = c->localRank;
@@ -136,19 +136,6 @@ ucclResult_t allGatherPushBegin(Comm* c, const void* shard, char* const* fullPee
   const char* src = static_cast<const char*>(shard);
   const size_t rowOff = static_cast<size_t>(me) * shardBytes;
   const int usedLanes = lanes > 0 ? std::min(lanes, n - 1) : 0;
-  // With lanes the data copies of a lane run back to back; each arrival flag is one more small copy
-  // in the same stream and costs a gap of its own.  flagStream moves the flag copies to a stream of
-  // their own (the last one, which no lane uses when n > lanes + 2), each behind an event recorded
-  // after its data copy, so the data stream never stops for a flag.
-  flagStream = flagStream && usedLanes > 0 && n - 1 > usedLanes + (copyOwn ? 1 : 0);
-  cudaStream_t fs = flagStream ? c->ceStream[n - 1] : nullptr;
-  if (flagStream) {
-    if (cudaStreamWaitEvent(fs, c->ceStart, 0) != cudaSuccess) return cudaFail(c, "cudaStreamWaitEvent");
-    for (int i = 0; i < kCeChunkEvents; ++i)
-      if (!c->ceChunkEvent[i] && cudaEventCreateWithFlags(&c->ceChunkEvent[i], cudaEventDisableTiming) != cudaSuccess)
-        return cudaFail(c, "cudaEventCreate");
-  }
-  int nextEvent = 0;
   auto pushChunk = [&](int p, int j, cudaStream_t st) -> ucclResult_t {
     const int b0 = static_cast<int>(static_cast<long long>(blocksPerRank) * j / chunks);
     const int b1 = static_cast<int>(static_cast<long long>(blocksPerRank) * (j + 1) / chunks);
@@ -156,14 +143,8 @@ ucclResult_t allGatherPushBegin(Comm* c, const void* shard, char* const* fullPee
     const size_t off = b0 * blkBytes, len = (b1 - b0) * blkBytes;
     if (cudaMemcpyAsync(fullPeer[p] + rowOff + off, src + off, len, cudaMemcpyDeviceToDevice, st) != cudaSuccess)
       return cudaFail(c, "cudaMemcpyAsync");
-    cudaStream_t flagSt = st;
-    if (flagStream && nextEvent < kCeChunkEvents) {
-      cudaEvent_t ev = c->ceChunkEvent[nextEvent++];
-      if (cudaEventRecord(ev, st) != cudaSuccess || cudaStreamWaitEvent(fs, ev, 0) != cudaSuccess) return cudaFail(c, "cudaEventRecord");
-      flagSt = fs;
-    }
     if (cudaMemcpyAsync(readyPeer[p] + (static_cast<size_t>(me) * blocksPerRank + b0) * kGemmFlagStrideBytes, c->onesDev,
-                        static_cast<size_t>(b1 - b0) * kGemmFlagStrideBytes, cudaMemcpyDeviceToDevice, flagSt) != cudaSuccess)
+                        static_cast<size_t>(b1 - b0) * kGemmFlagStrideBytes, cudaMemcpyDeviceToDevice, st) != cudaSuccess)
       return cudaFail(c, "cudaMemcpyAsync");
     return ucclSuccess;
   };
@@ -188,85 +169,13 @@ ucclResult_t allGatherPushBegin(Comm* c, const void* shard, char* const* fullPee
     return cudaFail(c, "cudaMemcpyAsync");
   return ucclSuccess;
 }
-ucclResult_t allGatherPushEnd(Comm* c, bool copyOwn, int lanes, bool flagStream, cudaStream_t s) {
+ucclResult_t allGatherPushEnd(Comm* c, bool copyOwn, int lanes, cudaStream_t s) {
   cudaStream_t streams[UCCL_MAX_LOCAL_RANKS + 1];
   const int nstreams = cePushStreams(c, lanes, copyOwn, streams);
-  const int n = c->localRanks;
-  const int usedLanes = lanes > 0 ? std::min(lanes, n - 1) : 0;
-  if (flagStream && usedLanes > 0 && n - 1 > usedLanes + (copyOwn ? 1 : 0)) {
-    if (cudaEventRecord(c->ceEvent[n - 1], c->ceStream[n - 1]) != cudaSuccess) return cudaFail(c, "cudaEventRecord");
-    if (cudaStreamWaitEvent(s, c->ceEvent[n - 1], 0) != cudaSuccess) return cudaFail(c, "cudaStreamWaitEvent");
-  }
   for (int i = 0; i < nstreams; ++i) {
     // one event per stream: the events array has an entry for every local rank
     if (cudaEventRecord(c->ceEvent[i], streams[i]) != cudaSuccess) return cudaFail(c, "cudaEventRecord");
     if (cudaStreamWaitEvent(s, c->ceEvent[i], 0) != cudaSuccess) return cudaFail(c, "cudaStreamWaitEvent");
-  }
-  return ucclSuccess;
-}
-
-// GEMM -> reduce-scatter by copy engines.  The kernel launched on `s` writes its partial results
-// for rank o into sendBuf[o] and raises slabFlag[q * chunks + ch] (q = position of o in the order
-// me+1, me+2, ...) when chunk ch of that slab is complete.  One side stream per peer waits for each
-// flag (a stream memory operation), copies the chunk into slot [me] of the peer's staging buffer
-// and then a one onto the peer's arrival flag [me][ch].
-//
-// Order of the three calls: Prepare, the kernel launch, Copies, End.  A stream parked on a memory
-// operation is invisible to CUDA's own dependency tracking, and streams share a limited number
-// of hardware queues: a kernel submitted behind such a wait in the same queue would never start,
-// and the wait would never end.  So nothing is parked before the kernel that raises the flags has
-// been submitted; afterwards a parked stream can at worst delay unrelated work until its flag
-// comes, which the running kernel guarantees.
-ucclResult_t reduceScatterPushPrepare(Comm* c, cudaStream_t s) {
-  ucclResult_t r = ensureCeStreams(c);
-  if (r != ucclSuccess) return r;
-  if ((r = ensureOnes(c)) != ucclSuccess) return r;
-  const DriverApi& d = driverApi();
-  if (!d.ok || !d.streamWaitValue64) {
-    commSetError(c, "stream memory operations are not available");
-    return ucclInvalidUsage;
-  }
-  // everything enqueued on `s` so far (the zeroing of the flags, the rank barrier) comes first
-  if (cudaEventRecord(c->ceStart, s) != cudaSuccess) return cudaFail(c, "cudaEventRecord");
-  return ucclSuccess;
-}
-ucclResult_t reduceScatterPushCopies(Comm* c, const char* sendBuf, char* const* stagePeer, char* const* ceDonePeer,
-                                     unsigned long long* slabFlag, size_t slabBytes, int chunks) {
-  const DriverApi& d = driverApi();
-  const int n = c->localRanks, me = c->localRank;
-  const size_t chunkBytes = slabBytes / chunks;
-  for (int q = 0; q + 1 < n; ++q) {
-    const int o = (me + 1 + q) % n;
-    cudaStream_t st = c->ceStream[o];
-    if (cudaStreamWaitEvent(st, c->ceStart, 0) != cudaSuccess) return cudaFail(c, "cudaStreamWaitEvent");
-    for (int ch = 0; ch < chunks; ++ch) {
-      const CUresult w = d.streamWaitValue64(reinterpret_cast<CUstream>(st),
-                                             reinterpret_cast<CUdeviceptr>(slabFlag + q * chunks + ch), 1,
-                                             CU_STREAM_WAIT_VALUE_GEQ);
-      if (w != CUDA_SUCCESS) {
-        commSetError(c, "cuStreamWaitValue64: %s", driverErrorString(w));
-        return ucclSystemError;
-      }
-      if (cudaMemcpyAsync(stagePeer[o] + static_cast<size_t>(me) * slabBytes + ch * chunkBytes,
-                          sendBuf + static_cast<size_t>(o) * slabBytes + ch * chunkBytes, chunkBytes,
-                          cudaMemcpyDeviceToDevice, st) != cudaSuccess)
-        return cudaFail(c, "cudaMemcpyAsync");
-      if (cudaMemcpyAsync(ceDonePeer[o] + static_cast<size_t>(me * chunks + ch) * kGemmFlagStrideBytes, c->onesDev,
-                          kGemmFlagStrideBytes, cudaMemcpyDeviceToDevice, st) != cudaSuccess)
-        return cudaFail(c, "cudaMemcpyAsync");
-    }
-  }
-  return ucclSuccess;
-}
-// After the kernel launch: once the kernel has ended - normally or not - every flag is raised so
-// that no side stream can be left waiting, then `s` waits for the side streams.
-ucclResult_t reduceScatterPushEnd(Comm* c, unsigned long long* slabFlag, int nflags, cudaStream_t s) {
-  if (cudaMemsetAsync(slabFlag, 0xff, sizeof(unsigned long long) * nflags, s) != cudaSuccess) return cudaFail(c, "cudaMemsetAsync");
-  const int n = c->localRanks, me = c->localRank;
-  for (int p = 0; p < n; ++p) {
-    if (p == me) continue;
-    if (cudaEventRecord(c->ceEvent[p], c->ceStream[p]) != cudaSuccess) return cudaFail(c, "cudaEventRecord");
-    if (cudaStreamWaitEvent(s, c->ceEvent[p], 0) != cudaSuccess) return cudaFail(c, "cudaStreamWaitEvent");
   }
   return ucclSuccess;
 }

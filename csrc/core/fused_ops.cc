@@ -75,29 +75,6 @@ int fusedAgMode(Comm* c) {
   return 1;
 }
 
-// Chunks per slab when the GEMM -> reduce-scatter fusion should use copy engines, 0 when the
-// epilogue should store to the owners itself.  UCCL_FUSED_RS=ce|kernel and UCCL_FUSED_RS_CHUNKS win
-// over ucclCommSetFusedRsOptions; the copy-engine form needs CTA pairs (rows per rank a multiple of
-// 256) and a chunk count that divides the row blocks of a rank.
-int fusedRsCeChunks(Comm* c, int blocksPerRank) {
-  int mode = c->fusedRsMode, chunks = c->fusedRsChunks;
-  if (const char* s = getenv("UCCL_FUSED_RS")) {
-    if (!strcasecmp(s, "ce") || !strcasecmp(s, "copy_engine")) mode = 2;
-    else if (!strcasecmp(s, "kernel")) mode = 1;
-  }
-  if (const char* s = getenv("UCCL_FUSED_RS_CHUNKS")) {
-    if (atoi(s) > 0) chunks = atoi(s);
-  }
-  if (mode != 2 || c->localRanks < 2 || blocksPerRank % 2 != 0) return 0;
-  if (const char* s = getenv("UCCL_GEMM_PAIR")) {
-    if (*s && atoi(s) == 0) return 0;
-  }
-  if (chunks <= 0) chunks = 4;
-  chunks = std::min(std::min(chunks, kGemmMaxCeChunks), blocksPerRank / 2);
-  while (chunks > 1 && (blocksPerRank % chunks != 0 || (blocksPerRank / chunks) % 2 != 0)) --chunks;
-  return std::max(chunks, 1);
-}
-
 // UCCL_FUSED_SELF=1 runs the fused kernels on a one-rank communicator too (every "peer" is this
 // GPU): the whole data path of the fusion in a single process, for profiling one kernel alone.
 bool fusedSelf() {
@@ -297,28 +274,17 @@ extern "C" ucclResult_t ucclAllGatherGemm(const void* xShard, void* xFull, const
     // 530 us with two, 559 us with a stream per peer)
     int lanes = c->fusedAgMode == 0 ? (n > 2 ? 1 : 0) : c->fusedCommCtas;
     if (const char* e = getenv("UCCL_FUSED_CE_LANES")) lanes = atoi(e);
-    // 32 + k lanes: k lanes, and the arrival flags travel on a stream of their own
-    bool flagStream = lanes >= 32;
-    if (flagStream) lanes -= 32;
-    if (const char* e = getenv("UCCL_FUSED_CE_FLAG_STREAM")) flagStream = atoi(e) != 0;
     if (lanes < 0 || n <= 2) lanes = 0;
     f.a_peer_major = lanes > 0 ? 1 : 0;
-    if ((r = allGatherPushBegin(c, xShard, fullPeer, readyPeer, shardBytes, rows / 128, !f.a_inplace, lanes, flagStream, s)) != ucclSuccess)
+    if ((r = allGatherPushBegin(c, xShard, fullPeer, readyPeer, shardBytes, rows / 128, !f.a_inplace, lanes, s)) != ucclSuccess)
       return r;
     if ((r = launchGemmBf16(g, &f, s)) != ucclSuccess) return r;
-    return allGatherPushEnd(c, !f.a_inplace, lanes, flagStream, s);
+    return allGatherPushEnd(c, !f.a_inplace, lanes, s);
   }
   commCount(c, ucclCollAllGather, static_cast<size_t>(M) * K * 2, ucclAlgoOneShot);
   f.a_spread = agMode == 3 ? 1 : 0;
-  // Forwarder warps (or the warps of the communication CTAs) store through the switch when xFull has a multicast alias: one store stream
-  // that the switch replicates, instead of nranks - 1 unicast copies.  Between two GPUs there is
-  // nothing to replicate and plain peer stores are faster.  UCCL_FUSED_AG_MC=0/1 overrides.
-  bool viaSwitch = sf.seg->mc != nullptr && n > 2 && c->forcedAlgo != ucclAlgoTwoShot && c->forcedAlgo != ucclAlgoOneShot;
-  if (const char* e = getenv("UCCL_FUSED_AG_MC")) viaSwitch = sf.seg->mc != nullptr && atoi(e) != 0;
-  if (viaSwitch) f.a_full_mc = sf.seg->mc + sf.off;
-  // The kernel reads my rows from the shard; they reach xFull through the switch with everybody
-  // else's copy, or else a copy engine puts them there meanwhile.
-  const bool sideCopy = !f.a_inplace && !viaSwitch;
+  // The kernel reads my rows from the shard; a copy engine puts them into xFull meanwhile.
+  const bool sideCopy = !f.a_inplace;
   if (sideCopy && (r = sideCopyBegin(c, const_cast<char*>(myRows), xShard, shardBytes, s)) != ucclSuccess) return r;
   if ((r = launchGemmBf16(g, &f, s)) != ucclSuccess) return r;
   if (sideCopy) return sideCopyEnd(c, s);
@@ -374,79 +340,6 @@ extern "C" ucclResult_t ucclGemmReduceScatter(const void* A, const void* W, void
   int reducers = c->fusedRsReducers;
   if (const char* e = getenv("UCCL_FUSED_RS_REDUCERS")) reducers = atoi(e);
   if (reducers < 0 || reducers > 64) reducers = 0;
-  const int rsChunks = fusedRsCeChunks(c, M / n / 128);
-  if (rsChunks > 0) {
-    // ---- copy engines carry the slabs (see reduceScatterPushCopies)
-    // the kernel must be loaded before any side stream is parked on a flag that only it can raise
-    if ((r = preloadGemmKernels()) != ucclSuccess) return r;
-    const size_t slabBytes = static_cast<size_t>(M / n) * N * 2;
-    const size_t need = static_cast<size_t>(M) * N * 2;
-    if (c->rsSendBytes < need) {
-      if (cudaStreamSynchronize(s) != cudaSuccess) return ucclSystemError;  // an earlier launch may still use the old buffer
-      if (c->rsSendBuf) cudaFree(c->rsSendBuf);
-      c->rsSendBuf = nullptr;
-      c->rsSendBytes = 0;
-      if (cudaMalloc(&c->rsSendBuf, need) != cudaSuccess) {
-        commSetError(c, "out of memory for the %zu-byte reduce-scatter send buffer", need);
-        return ucclSystemError;
-      }
-      c->rsSendBytes = need;
-    }
-    if (!c->rsCtl) {
-      if (cudaMalloc(&c->rsCtl, 4096) != cudaSuccess) return ucclSystemError;
-      // run once, here, the very memset that reduceScatterPushEnd issues while side streams are
-      // parked: whatever it needs loaded is loaded now
-      if (cudaMemsetAsync(static_cast<char*>(c->rsCtl) + 1024, 0xff, sizeof(unsigned long long) * (n - 1) * rsChunks, s) != cudaSuccess)
-        return ucclSystemError;
-    }
-    uint32_t* slabCount = static_cast<uint32_t*>(c->rsCtl);
-    unsigned long long* slabFlag = reinterpret_cast<unsigned long long*>(static_cast<char*>(c->rsCtl) + 1024);
-    char* ceDone = c->arena->local + kArenaGemmCeDoneOff;
-    if (cudaMemsetAsync(c->rsCtl, 0, 4096, s) != cudaSuccess ||
-        cudaMemsetAsync(ceDone, 0, kGemmFlagStrideBytes * n * rsChunks, s) != cudaSuccess)
-      return ucclSystemError;
-    if (!fold && (r = enqueueBarrier(c, s)) != ucclSuccess) return r;
-    GemmFusion f;
-    if (fold) {
-      f.arena_peer = c->dev.arena;
-      f.epochs = c->dev.epochs;
-      f.go = go;
-    }
-    f.role = 3;
-    f.tail_next = tailNext;
-    f.rs_reducers = reducers;
-    f.rank = c->localRank;
-    f.nranks = n;
-    f.timeout_ns = c->dev.timeoutNs;
-    f.abort_flag = c->dev.abortFlag;
-    f.rows_per_rank = M / n;
-    char* stagePeer[UCCL_MAX_LOCAL_RANKS];
-    char* ceDonePeer[UCCL_MAX_LOCAL_RANKS];
-    for (int p = 0; p < n; ++p) {
-      f.stage_peer[p] = stagePeer[p] = sp.seg->peer[p] + sp.off;
-      f.done_peer[p] = reinterpret_cast<uint32_t*>(c->arena->peer[p] + kArenaGemmDoneOff);
-      ceDonePeer[p] = c->arena->peer[p] + kArenaGemmCeDoneOff;
-    }
-    f.done_peer[c->localRank] = done;
-    f.slab_count = slabCount;
-    f.slab_flag = slabFlag;
-    f.ce_done = reinterpret_cast<const uint32_t*>(ceDone);
-    f.ce_chunks = rsChunks;
-    f.rs_out = out;
-    f.rs_ldo = N;
-    g.C = c->rsSendBuf;
-    commCount(c, ucclCollReduceScatter, static_cast<size_t>(M) * N * 2, ucclAlgoCopyEngine);
-    if ((r = reduceScatterPushPrepare(c, s)) != ucclSuccess) return r;
-    if ((r = launchGemmBf16(g, &f, s)) != ucclSuccess) return r;
-    // only now, with the kernel that raises the flags submitted, are the side streams parked on them
-    r = reduceScatterPushCopies(c, static_cast<const char*>(c->rsSendBuf), stagePeer, ceDonePeer, slabFlag, slabBytes, rsChunks);
-    if (r != ucclSuccess) {
-      // release whatever was parked before the failure, then report it
-      (void)reduceScatterPushEnd(c, slabFlag, (n - 1) * rsChunks, s);
-      return r;
-    }
-    return reduceScatterPushEnd(c, slabFlag, (n - 1) * rsChunks, s);
-  }
   if (!fold && (r = enqueueBarrier(c, s)) != ucclSuccess) return r;
   GemmFusion f;
   if (fold) {

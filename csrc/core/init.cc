@@ -406,11 +406,7 @@ void destroyComm(Comm* c) {
       if (c->ceEvent[i]) cudaEventDestroy(c->ceEvent[i]);
     }
     if (c->ceStart) cudaEventDestroy(c->ceStart);
-    for (cudaEvent_t e : c->ceChunkEvent)
-      if (e) cudaEventDestroy(e);
     if (c->onesDev) cudaFree(c->onesDev);
-    if (c->rsSendBuf) cudaFree(c->rsSendBuf);
-    if (c->rsCtl) cudaFree(c->rsCtl);
     if (c->netScratch) cudaFree(c->netScratch);
     if (c->epochsDev) cudaFree(c->epochsDev);
     if (c->hostFlags) cudaFreeHost(c->hostFlags);
@@ -610,15 +606,6 @@ extern "C" ucclResult_t ucclCommSetFusedOptions(ucclComm_t comm, int agMode, int
   c->fusedAgMode = agMode;
   c->fusedCommCtas = commCtas;
   c->fusedCeChunks = ceChunks;
-  return ucclSuccess;
-}
-
-extern "C" ucclResult_t ucclCommSetFusedRsOptions(ucclComm_t comm, int rsMode, int ceChunks) {
-  Comm* c = toComm(comm);
-  if (!commValid(c)) return ucclInvalidArgument;
-  if (rsMode < 0 || rsMode > 2 || ceChunks < 0 || ceChunks > kGemmMaxCeChunks) return ucclInvalidArgument;
-  c->fusedRsMode = rsMode;
-  c->fusedRsChunks = ceChunks;
   return ucclSuccess;
 }
 

@@ -362,6 +362,11 @@ TuneChoice Tuner::prior(const TuneQuery& q) const {
       c.algo = (nvls && q.bytes > (64u << 10)) ? ucclAlgoNvls : ucclAlgoTwoShot;
       if (q.coll == ucclCollReduce && !nvls) c.algo = ucclAlgoOneShot;
       break;
+    case ucclCollAllToAll:
+      // pure copies, nothing to reduce: one CTA per 128 KiB of the message
+      c.algo = ucclAlgoTwoShot;
+      c.blocks = static_cast<int>(std::min<size_t>(48, std::max<size_t>(c.blocks, q.bytes >> 17)));
+      break;
     default:
       c.algo = ucclAlgoTwoShot;
       break;

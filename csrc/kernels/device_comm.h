@@ -13,16 +13,16 @@ constexpr int kLLBlocks = 16;         // CTAs the low-latency protocol may use
 constexpr int kLLDataPerBlock = 4096; // payload bytes per CTA per peer per LL operation
 constexpr int kLLSlotBytes = 2 * kLLDataPerBlock;  // each 8 data bytes travel with 8 flag bytes
 constexpr int kP2pSlots = 4;               // FIFO depth per stripe: four pieces in flight hide the credit round trip
-constexpr size_t kP2pSlotBytes = 1u << 20;  // one slot of every stripe together (128 KiB per stripe)
+constexpr size_t kP2pSlotBytes = 4u << 20;  // one slot of every stripe together (128 KiB per stripe)
 
 // Arena layout (byte offsets inside every rank's symmetric arena).
-constexpr size_t kArenaBarrierOff = 0;                 // u32 [kMaxBlocks][UCCL_MAX_LOCAL_RANKS]
+constexpr size_t kArenaBarrierOff = 0;                 // u32 [kMaxBlocks][kBarrierSlotWords]: one 128-byte line per CTA, word r written by rank r
+constexpr int kBarrierSlotWords = 32;
+static_assert(UCCL_MAX_LOCAL_RANKS <= kBarrierSlotWords, "a CTA's barrier words must fit one line");
 // fused GEMM flags: one 128-byte line per 128-row block (see FLAG_STRIDE in gemm_sm100.cuh)
 constexpr size_t kGemmFlagStrideBytes = 128;
 constexpr int kGemmMaxRowBlocks = 1024;
-constexpr int kGemmMaxCeChunks = 8;
 constexpr size_t kArenaGemmReadyOff = 512u << 10;      // all-gather arrival counters, 128 KiB
-constexpr size_t kArenaGemmCeDoneOff = 640u << 10;     // reduce-scatter by copy engines: [rank][chunk] arrival flags, 16 KiB
 constexpr size_t kArenaGemmDoneOff = 768u << 10;       // reduce-scatter counters, 128 KiB
 constexpr size_t kArenaP2pCtrlOff = 96u << 10;         // P2pCtrl [UCCL_MAX_LOCAL_RANKS][kP2pStripes]
 constexpr size_t kArenaMoeCtrlOff = 128u << 10;        // MoE counters (see moe.cu)
@@ -52,7 +52,18 @@ struct RingCtrl {
 // Control words of the point-to-point FIFOs between this rank and one peer, for one stripe; the
 // arena holds P2pCtrl [UCCL_MAX_LOCAL_RANKS][kP2pStripes] indexed by peer.  All four counters
 // count slots since communicator creation.
-constexpr int kP2pStripes = 8;  // CTAs (and independent sub-FIFOs) per point-to-point operation
+constexpr int kP2pStripes = 32;  // CTAs (and independent sub-FIFOs) a point-to-point operation may use
+// Stripes an operation of `bytes` bytes is cut into: one per 32 KiB, so that a small message costs
+// one CTA and a large one gets them all.  Sender and receiver compute it from the same byte count.
+#ifdef __CUDACC__
+#define UCCL_HOST_DEVICE __host__ __device__
+#else
+#define UCCL_HOST_DEVICE
+#endif
+inline UCCL_HOST_DEVICE int p2pStripesFor(size_t bytes) {
+  const size_t s = bytes >> 15;
+  return s < 1 ? 1 : (s > static_cast<size_t>(kP2pStripes) ? kP2pStripes : static_cast<int>(s));
+}
 struct P2pCtrl {
   uint64_t tail;  // written remotely by the peer when it is the sender: slots it has filled for me
   uint64_t head;  // written remotely by the peer when it is the receiver: slots of mine it has drained

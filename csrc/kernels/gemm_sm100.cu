@@ -126,36 +126,7 @@ bool usePairKernel() {
   return (s && *s) ? atoi(s) != 0 : true;
 }
 
-template <int EPI, int COMM>
-cudaError_t loadVariants() {
-  static thread_local int last1 = -1, last2 = -1;
-  static thread_local cudaError_t e1 = cudaSuccess, e2 = cudaSuccess;
-  cudaError_t e = ensureSmem(gemm::gemm_bf16_kernel<EPI, COMM>, &last1, &e1);
-  if (e != cudaSuccess) return e;
-  return ensureSmem(gemm::gemm2_bf16_kernel<EPI, COMM>, &last2, &e2);
-}
-
 }  // namespace
-
-ucclResult_t preloadGemmKernels() {
-  cudaError_t e = loadVariants<gemm::kEpiStore, gemm::kCommNone>();
-  if (e == cudaSuccess) e = loadVariants<gemm::kEpiSwiGLU, gemm::kCommNone>();
-  if (e == cudaSuccess) e = loadVariants<gemm::kEpiStore, gemm::kCommAllGather>();
-  if (e == cudaSuccess) e = loadVariants<gemm::kEpiSwiGLU, gemm::kCommAllGather>();
-  if (e == cudaSuccess) e = loadVariants<gemm::kEpiStore, gemm::kCommReduceScatter>();
-  if (e == cudaSuccess) {
-    static thread_local int last = -1;
-    static thread_local cudaError_t err = cudaSuccess;
-    e = ensureSmem(gemm::gemm2_bf16_kernel<gemm::kEpiStore, gemm::kCommReduceScatterCe>, &last, &err);
-  }
-  if (e != cudaSuccess) {
-    UCCL_LOG(ERROR, "loading the GEMM kernels failed: %s", cudaGetErrorString(e));
-    (void)cudaGetLastError();
-    return ucclSystemError;
-  }
-  (void)maxResidentPairs();
-  return ucclSuccess;
-}
 
 ucclResult_t launchGemmBf16(const GemmLaunch& g, const GemmFusion* f, cudaStream_t stream) {
   if (!g.A || !g.B || !g.C || g.M <= 0 || g.N <= 0 || g.K <= 0) return ucclInvalidArgument;
@@ -164,7 +135,7 @@ ucclResult_t launchGemmBf16(const GemmLaunch& g, const GemmFusion* f, cudaStream
     return ucclInvalidArgument;
   if (g.epilogue == gemm::kEpiSwiGLU && (g.N % 2 != 0)) return ucclInvalidArgument;
   const int role = f ? f->role : 0;
-  if ((role == gemm::kCommReduceScatter || role == gemm::kCommReduceScatterCe) && g.epilogue != gemm::kEpiStore)
+  if (role == gemm::kCommReduceScatter && g.epilogue != gemm::kEpiStore)
     return ucclInvalidArgument;
 
   CUtensorMap tmA, tmB;
@@ -218,7 +189,7 @@ ucclResult_t launchGemmBf16(const GemmLaunch& g, const GemmFusion* f, cudaStream
       // the fused kernels' own barrier slot: the last CTA index a collective may use
       constexpr int kSlot = kMaxBlocks - 1;
       for (int i = 0; i < f->nranks; ++i)
-        c.bar_row_peer[i] = reinterpret_cast<uint32_t*>(f->arena_peer[i] + kArenaBarrierOff) + kSlot * UCCL_MAX_LOCAL_RANKS;
+        c.bar_row_peer[i] = reinterpret_cast<uint32_t*>(f->arena_peer[i] + kArenaBarrierOff) + kSlot * kBarrierSlotWords;
       c.bar_epoch = f->epochs + kSlot;
       c.go = f->go;
     }
@@ -231,14 +202,13 @@ ucclResult_t launchGemmBf16(const GemmLaunch& g, const GemmFusion* f, cudaStream
         c.ready_peer[i] = f->ready_peer[i];
       }
       c.a_shard = static_cast<const char*>(f->a_shard);
-      c.a_full_mc = static_cast<char*>(f->a_full_mc);
       c.a_inplace = f->a_inplace;
       a.a_ready = f->ready_peer[f->rank];
       // one count per copied piece of a row block (see comm_allgather_push / _push2d)
       const size_t blkBytes = static_cast<size_t>(gemm::BM) * g.K * 2;
       a.a_spread = (!f->a_external && f->a_spread) ? 1 : 0;
       if (f->a_external) a.a_ready_target = 1;
-      else if (a.a_spread || f->a_full_mc) a.a_ready_target = static_cast<uint32_t>((blkBytes + gemm::FWD_SLOT_BYTES - 1) / gemm::FWD_SLOT_BYTES);
+      else if (a.a_spread) a.a_ready_target = static_cast<uint32_t>((blkBytes + gemm::FWD_SLOT_BYTES - 1) / gemm::FWD_SLOT_BYTES);
       else a.a_ready_target = static_cast<uint32_t>((blkBytes + gemm::COPY_SLOT_BYTES - 1) / gemm::COPY_SLOT_BYTES);
       a.a_local_lo = f->rank * blk_per_rank;
       a.a_local_hi = a.a_local_lo + blk_per_rank;
@@ -248,23 +218,6 @@ ucclResult_t launchGemmBf16(const GemmLaunch& g, const GemmFusion* f, cudaStream
         if (!makeTensorMap(&pm.m[0], f->a_shard, f->rows_per_rank, g.K, g.K, gemm::BK, gemm::BM)) return ucclSystemError;
       }
       a.m_order = (a.debug & 4) ? 0 : (f->a_peer_major ? 3 : 1);  // debug is zero outside experiment builds
-    } else if (role == gemm::kCommReduceScatterCe) {
-      // copy engines carry the slabs: the kernel only writes local memory and counts
-      if (!usePairKernel() || f->rows_per_rank % (2 * gemm::BM) != 0 || f->ce_chunks < 1 ||
-          blk_per_rank % f->ce_chunks != 0 || (blk_per_rank / f->ce_chunks) % 2 != 0 || g.ldc != g.N)
-        return ucclInvalidArgument;
-      c.done_peer[f->rank] = f->done_peer[f->rank];
-      c.stage_local = static_cast<const char*>(f->stage_peer[f->rank]);
-      c.slab_count = f->slab_count;
-      c.slab_flag = f->slab_flag;
-      c.ce_done = f->ce_done;
-      c.ce_chunks = f->ce_chunks;
-      c.slab_target = static_cast<uint32_t>((blk_per_rank / f->ce_chunks) * a.tiles_n * 4);
-      c.own_target = static_cast<uint32_t>(a.tiles_n * 4);
-      c.rs_out = static_cast<char*>(f->rs_out);
-      c.rs_ldo = f->rs_ldo;
-      c.tail_next = f->tail_next;
-      a.m_order = 4;
     } else {
       for (int i = 0; i < f->nranks; ++i) {
         c.done_peer[i] = f->done_peer[i];
@@ -285,18 +238,17 @@ ucclResult_t launchGemmBf16(const GemmLaunch& g, const GemmFusion* f, cudaStream
   // Epilogue through shared memory + TMA stores: whole 128-byte lines instead of one 16-byte piece
   // per lane and row.  Needs 64-column boxes to tile the output exactly; the unicast forwarder warp
   // of the all-gather fusion uses the same staging area, so that mode keeps the direct stores.
-  // UCCL_GEMM_EPI=lsu|tma overrides.
+  // (Experiment builds: UCCL_GEMM_EPI=lsu keeps the direct stores.)
   {
     const int outN = g.epilogue == gemm::kEpiSwiGLU ? g.N / 2 : g.N;
-    bool tma = outN % 64 == 0 && role != gemm::kCommReduceScatter && !(a.a_spread && !a.comm.a_full_mc);
+    bool tma = outN % 64 == 0 && role != gemm::kCommReduceScatter && !a.a_spread;
+#ifdef UCCL_EXPERIMENTS
     if (const char* e = getenv("UCCL_GEMM_EPI")) {
       if (!strcasecmp(e, "lsu")) tma = false;
     }
+#endif
     if (tma) {
       if (!makeTensorMap(&pm.m[gemm::kMaxPeers], g.C, g.M, outN, g.ldc, 64, 32)) return ucclSystemError;
-      if (role == gemm::kCommReduceScatterCe &&
-          !makeTensorMap(&pm.m[0], f->stage_peer[f->rank], static_cast<uint64_t>(f->nranks) * f->rows_per_rank, g.N, g.N, 64, 32))
-        return ucclSystemError;
       a.epi_tma = 1;
     }
   }
@@ -316,7 +268,7 @@ ucclResult_t launchGemmBf16(const GemmLaunch& g, const GemmFusion* f, cudaStream
     // reducer CTAs (reduce-scatter only, and only with the shared work counter) come out of the
     // resident budget: they must run from the start, next to the GEMM CTAs
     int reducers = 0;
-    if ((role == gemm::kCommReduceScatter || role == gemm::kCommReduceScatterCe) && f->tail_next && f->rs_reducers > 0)
+    if (role == gemm::kCommReduceScatter && f->tail_next && f->rs_reducers > 0)
       reducers = std::min(f->rs_reducers & ~1, maxPairs & ~1);  // whole clusters, at most half of the resident CTAs
     int pairs = std::max(1, std::min(maxPairs - comm_ctas / 2 - reducers / 2, tiles2));
     a.gemm_ctas = 2 * pairs;
@@ -327,7 +279,6 @@ ucclResult_t launchGemmBf16(const GemmLaunch& g, const GemmFusion* f, cudaStream
     } else {
       if (role == gemm::kCommAllGather) e = launchPairT<gemm::kEpiStore, gemm::kCommAllGather>(tmA, tmB, pm, a, grid, stream);
       else if (role == gemm::kCommReduceScatter) e = launchPairT<gemm::kEpiStore, gemm::kCommReduceScatter>(tmA, tmB, pm, a, grid, stream);
-      else if (role == gemm::kCommReduceScatterCe) e = launchPairT<gemm::kEpiStore, gemm::kCommReduceScatterCe>(tmA, tmB, pm, a, grid, stream);
       else e = launchPairT<gemm::kEpiStore, gemm::kCommNone>(tmA, tmB, pm, a, grid, stream);
     }
   } else {

@@ -26,8 +26,7 @@
 //       has been read, and the owner's counter for the row block is bumped one tile later, when
 //       the stores have completed.  When its tiles are done every CTA helps to sum the n staged
 //       copies of this rank's own rows in fp32 (local loads only) into the output.  No SM is
-//       reserved for communication.  In the copy-engine variant the epilogue only writes local
-//       memory and counts finished chunks; side streams carry them (reduceScatterPushCopies).
+//       reserved for communication.
 // Every TMA load writes only the shared memory of the CTA that issued it; peers' memory is
 // reached with plain (non-replicating) bulk copies.
 //
@@ -89,7 +88,6 @@ enum CommRole : int {
   kCommNone = 0,
   kCommAllGather = 1,
   kCommReduceScatter = 2,    // epilogue TMA-stores tiles into the owners' staging slots
-  kCommReduceScatterCe = 3,  // epilogue stores locally, copy engines carry finished slabs to their owners
 };
 
 constexpr int kMaxPeers = 16;
@@ -103,7 +101,7 @@ struct CommArgs {
   uint64_t timeout_ns = 0;         // deadline for cross-rank waits
   uint32_t* abort_flag = nullptr;  // comm-wide abort word (device-visible)
   // rank barrier folded into the launch: GEMM CTA 0 meets CTA 0 of every rank, then raises `go`;
-  // nothing is written to a peer and no flag is raised for a copy engine before that
+  // nothing is written to a peer before that
   uint32_t* bar_row_peer[kMaxPeers] = {};  // every rank's barrier words of the fused kernels' slot, indexed by source rank
   uint32_t* bar_epoch = nullptr;            // local: barriers done so far on that slot
   uint32_t* go = nullptr;                   // local, zero at launch: 1 = every rank has arrived, 2 = gave up; nullptr = no folded barrier
@@ -113,20 +111,10 @@ struct CommArgs {
   const char* a_shard = nullptr;
   int a_inplace = 0;
   char* a_full_peer[kMaxPeers] = {};
-  char* a_full_mc = nullptr;   // multicast alias of A_full (NVSwitch replicates one store to every rank) or nullptr
   uint32_t* ready_peer[kMaxPeers] = {};  // every rank's arrival counters, one per 128-row block, zero at launch
   // reduce-scatter: every rank owns a staging buffer [nranks][rows_per_rank][N]; slot s receives
   // rank s's partial result for the owner's rows (tensor maps in PeerMaps)
   const char* stage_local = nullptr;
-  // copy-engine variant: partial tiles for other ranks go to a local send buffer (Args.C); per
-  // chunk of a slab a counter of finished (warp, tile) pairs and a 64-bit flag that a side
-  // stream waits on; per (source rank, chunk) an arrival flag that the source's copy engine sets
-  uint32_t* slab_count = nullptr;             // local [(nranks - 1) * ce_chunks]
-  unsigned long long* slab_flag = nullptr;    // local [(nranks - 1) * ce_chunks]
-  const uint32_t* ce_done = nullptr;          // local, FLAG_STRIDE apart: [nranks * ce_chunks]
-  int ce_chunks = 1;                          // chunks per slab; divides the row blocks per rank
-  uint32_t slab_target = 0;                   // (warp, tile) pairs per chunk
-  uint32_t own_target = 0;                    // (warp, tile) pairs per own row block
   uint32_t* done_peer[kMaxPeers] = {};  // every rank's per-row-block counters, zero at launch
   uint32_t done_target = 0;             // nranks * column tiles
   char* rs_out = nullptr;               // [rows_per_rank, N] bf16
@@ -249,13 +237,6 @@ __device__ __forceinline__ int order_rows(const Args& a, int m, int tiles_rows, 
     if (m < bpr) return r * bpr + m;
     const int i = m - bpr, j = i / (n - 1), q = i % (n - 1) + 1;
     return ((r + q) % n) * bpr + j;
-  }
-  if (a.m_order == 4) {
-    // reduce-scatter by copy engines: the slab of rank r+1 first, then r+2, ..., my own last, so
-    // that finished slabs travel while the later ones are computed
-    const int bpr = a.m_bpr / unit, n = a.comm.nranks, r = a.comm.rank;
-    const int q = m / bpr, j = m - q * bpr;
-    return ((r + 1 + q) % n) * bpr + j;
   }
   if (a.m_order == 3) {
     // all-gather by copy-engine lanes: my own shard, then the whole shard of rank r+1, r+2, ...
@@ -396,62 +377,6 @@ __device__ void comm_allgather_push(const Args& a, uint8_t* smem, uint64_t* bars
   }
   ptx::tma_store_wait<0>();
   for (int i = total > LAG ? total - LAG : 0; i < total; ++i) completed(i);
-  flush();
-}
-
-// ------------------------------------------------------------------ all-gather push through the switch
-// Forwarder warp of "spread" mode when A_full has a multicast alias: the 32 lanes read this CTA's
-// share of the shard with 16-byte loads and write it with multimem.st, which the switch
-// replicates into every rank's A_full (this rank's own copy included).  One store stream instead
-// of nranks - 1 unicast copies: the SM that also runs the GEMM issues a seventh of the stores at
-// eight ranks.  Pieces and counting are those of comm_allgather_push with FWD_SLOT_BYTES pieces:
-// one add per (row block, rank) covering this CTA's pieces of the block.
-__device__ void comm_allgather_push_mc(const Args& a, int cta, int nctas, int lane) {
-  const CommArgs& c = a.comm;
-  const int n = c.nranks, r = c.rank, bpr = a.m_bpr;
-  const size_t blkBytes = static_cast<size_t>(BM) * a.K * 2;
-  const int nsub = static_cast<int>((blkBytes + FWD_SLOT_BYTES - 1) / FWD_SLOT_BYTES);
-  const int allPieces = bpr * nsub;
-  const size_t shardOff = static_cast<size_t>(r) * bpr * blkBytes;
-  int curBlk = -1;
-  uint32_t cnt = 0;
-  auto flush = [&]() {
-    if (curBlk < 0 || cnt == 0) return;
-    // every lane orders its own stores, then lane 0 publishes the count
-    ptx::fence_sys();
-    __syncwarp();
-    if (lane == 0) {
-      for (int q = 1; q < n; ++q) {
-        const int p = (r + q) % n;
-        ptx::red_release_sys_add_u32(c.ready_peer[p] + static_cast<size_t>(r * bpr + curBlk) * FLAG_STRIDE, cnt);
-      }
-    }
-    cnt = 0;
-  };
-  for (int g = cta; g < allPieces; g += nctas) {
-    const int blk = g / nsub, sub = g - blk * nsub;
-    if (blk != curBlk) {
-      flush();
-      curBlk = blk;
-    }
-    const size_t off = static_cast<size_t>(blk) * blkBytes + static_cast<size_t>(sub) * FWD_SLOT_BYTES;
-    const size_t left = blkBytes - static_cast<size_t>(sub) * FWD_SLOT_BYTES;
-    const uint32_t bytes = static_cast<uint32_t>(left < FWD_SLOT_BYTES ? left : FWD_SLOT_BYTES);
-    const char* src = c.a_shard + off;
-    char* dst = c.a_full_mc + shardOff + off;
-    // blkBytes is a multiple of 16 (K % 8 == 0): whole vectors only; four loads in flight per lane
-    uint32_t i = static_cast<uint32_t>(lane) << 4;
-    for (; i + 3 * 512 < bytes; i += 4 * 512) {
-      const uint4 v0 = ptx::ld_global_v4(src + i), v1 = ptx::ld_global_v4(src + i + 512);
-      const uint4 v2 = ptx::ld_global_v4(src + i + 1024), v3 = ptx::ld_global_v4(src + i + 1536);
-      ptx::multimem_st_v4(dst + i, v0);
-      ptx::multimem_st_v4(dst + i + 512, v1);
-      ptx::multimem_st_v4(dst + i + 1024, v2);
-      ptx::multimem_st_v4(dst + i + 1536, v3);
-    }
-    for (; i < bytes; i += 512) ptx::multimem_st_v4(dst + i, ptx::ld_global_v4(src + i));
-    ++cnt;
-  }
   flush();
 }
 
@@ -612,7 +537,7 @@ __device__ __forceinline__ void tail_sum_piece(const uint8_t* sbase, uint32_t P,
 // from shared memory and write the bf16 result.  192 KiB of loads in flight per SM without
 // holding them in registers.
 __device__ void reduce_scatter_tail(const Args& a, uint8_t* smem, uint64_t* tbars, volatile uint32_t* bail, int cta,
-                                    int nctas, bool ce) {
+                                    int nctas) {
   const CommArgs& c = a.comm;
   const int n = c.nranks, bpr = a.m_bpr;
   constexpr int TSTAGES = 3;
@@ -650,31 +575,12 @@ __device__ void reduce_scatter_tail(const Args& a, uint8_t* smem, uint64_t* tbar
     for (int i = 0; i < TSTAGES; ++i) ptx::mbar_init(&tbars[i], 1);
     ptx::mbar_fence_init();
   }
-  // Row block b of mine is complete when, TMA variant: its counter has every rank's tiles;
-  // copy-engine variant: my own tiles are counted and every other rank's copy engine has set the
-  // flag of the chunk that holds the block.
-  const uint32_t ownTarget = ce ? c.own_target : c.done_target;
-  const int blocksPerChunk = ce ? bpr / c.ce_chunks : 1;
+  // Row block b of mine is complete when its counter has every rank's tiles.
   auto peek = [&](int b) -> bool {
-    if (ptx::ld_relaxed_sys_u32(done + static_cast<size_t>(b) * FLAG_STRIDE) < ownTarget) return false;
-    if (ce) {
-      const int ch = b / blocksPerChunk;
-      for (int p = 0; p < n; ++p)
-        if (p != c.rank && ptx::ld_relaxed_sys_u32(c.ce_done + static_cast<size_t>(p * c.ce_chunks + ch) * FLAG_STRIDE) < 1u)
-          return false;
-    }
-    return true;
+    return ptx::ld_relaxed_sys_u32(done + static_cast<size_t>(b) * FLAG_STRIDE) >= c.done_target;
   };
   auto await = [&](int b) -> bool {  // bounded; thread 0 only
-    if (!wait_flag_geq(done + static_cast<size_t>(b) * FLAG_STRIDE, ownTarget, c.timeout_ns, c.abort_flag)) return false;
-    if (ce) {
-      const int ch = b / blocksPerChunk;
-      for (int p = 0; p < n; ++p)
-        if (p != c.rank && !wait_flag_geq(c.ce_done + static_cast<size_t>(p * c.ce_chunks + ch) * FLAG_STRIDE, 1u,
-                                          c.timeout_ns, c.abort_flag))
-          return false;
-    }
-    return true;
+    return wait_flag_geq(done + static_cast<size_t>(b) * FLAG_STRIDE, c.done_target, c.timeout_ns, c.abort_flag);
   };
   // every thread looks at one row block; the loader takes the complete prefix
   uint32_t* s_ready = reinterpret_cast<uint32_t*>(smem);  // [bpr] flags, shared memory is idle here
@@ -952,15 +858,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PIPE_BYTES + EPI_STAGE_BYTES);
   if (COMM == kCommAllGather && static_cast<int>(blockIdx.x) < a.comm_ctas) {
-    if (a.comm.a_full_mc) {
-      // through the switch: every warp of the communication CTAs is a pusher of its own
-      const int w = threadIdx.x >> 5, nw = blockDim.x >> 5, l = threadIdx.x & 31;
-      int g = 1;
-      if (l == 0) g = wait_go(a.comm) ? 1 : 0;
-      g = __shfl_sync(0xffffffffu, g, 0);
-      if (g && !UCCL_DBG(a, 1)) comm_allgather_push_mc(a, static_cast<int>(blockIdx.x) * nw + w, a.comm_ctas * nw, l);
-      return;
-    }
     if (!UCCL_DBG(a, 1) && threadIdx.x == 0 && wait_go(a.comm))
       comm_allgather_push<COPY_SLOT_BYTES, COPY_SLOTS, 4, 4>(a, smem, bars, blockIdx.x, a.comm_ctas);
     return;
@@ -971,7 +868,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     volatile uint32_t* rbail = reinterpret_cast<volatile uint32_t*>(bars + 28);
     if (threadIdx.x == 0) *rbail = 0;
     __syncthreads();
-    reduce_scatter_tail(a, smem, bars + 24, rbail, cta_id, a.gemm_ctas, false);
+    reduce_scatter_tail(a, smem, bars + 24, rbail, cta_id, a.gemm_ctas);
     return;
   }
   uint64_t* full_bar = bars;                     // [STAGES]
@@ -1092,8 +989,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (COMM == kCommAllGather && a.a_spread && lane == 0) go_ok = wait_go(a.comm) ? 1 : 0;
     go_ok = __shfl_sync(0xffffffffu, go_ok, 0);
     if (COMM == kCommAllGather && a.a_spread && !UCCL_DBG(a, 1) && go_ok) {
-      if (a.comm.a_full_mc) comm_allgather_push_mc(a, blockIdx.x, gridDim.x, lane);
-      else if (lane == 0) comm_allgather_push<FWD_SLOT_BYTES, FWD_SLOTS, 2, 2>(a, smem + PIPE_BYTES, bars + 24, blockIdx.x, gridDim.x);
+      if (lane == 0) comm_allgather_push<FWD_SLOT_BYTES, FWD_SLOTS, 2, 2>(a, smem + PIPE_BYTES, bars + 24, blockIdx.x, gridDim.x);
     }
   } else {
     // ------------------------------------------------------------ epilogue warps
@@ -1140,7 +1036,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (UCCL_TIMES(a) && cta_id == 0 && threadIdx.x == 0) a.times[1] = ptx::globaltimer_ns();
   if (COMM == kCommReduceScatter && !*bail && !UCCL_DBG(a, 1)) {
     if (UCCL_DBG(a, 128)) reduce_scatter_tail_direct(a, cta_id, gemm_ctas);
-    else reduce_scatter_tail(a, smem, bars + 24, bail, cta_id, gemm_ctas, false);
+    else reduce_scatter_tail(a, smem, bars + 24, bail, cta_id, gemm_ctas);
   }
 }
 
@@ -1165,27 +1061,18 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PIPE_BYTES + EPI_STAGE_BYTES);
   if (COMM == kCommAllGather && static_cast<int>(blockIdx.x) < a.comm_ctas) {
-    if (a.comm.a_full_mc) {
-      // through the switch: every warp of the communication CTAs is a pusher of its own
-      const int w = threadIdx.x >> 5, nw = blockDim.x >> 5, l = threadIdx.x & 31;
-      int g = 1;
-      if (l == 0) g = wait_go(a.comm) ? 1 : 0;
-      g = __shfl_sync(0xffffffffu, g, 0);
-      if (g && !UCCL_DBG(a, 1)) comm_allgather_push_mc(a, static_cast<int>(blockIdx.x) * nw + w, a.comm_ctas * nw, l);
-      return;
-    }
     if (!UCCL_DBG(a, 1) && threadIdx.x == 0 && wait_go(a.comm))
       comm_allgather_push<COPY_SLOT_BYTES, COPY_SLOTS, 4, 4>(a, smem, bars, blockIdx.x, a.comm_ctas);
     return;
   }
   const int cta_id = static_cast<int>(blockIdx.x) - a.comm_ctas;
-  if ((COMM == kCommReduceScatter || COMM == kCommReduceScatterCe) && cta_id >= a.gemm_ctas) {
+  if (COMM == kCommReduceScatter && cta_id >= a.gemm_ctas) {
     // reducer CTA (both CTAs of such a cluster, independently): sums the staged copies of this
     // rank's row blocks as they complete, from the start of the launch
     volatile uint32_t* rbail = reinterpret_cast<volatile uint32_t*>(bars + 28);
     if (threadIdx.x == 0) *rbail = 0;
     __syncthreads();
-    reduce_scatter_tail(a, smem, bars + 24, rbail, cta_id, a.gemm_ctas, COMM == kCommReduceScatterCe);
+    reduce_scatter_tail(a, smem, bars + 24, rbail, cta_id, a.gemm_ctas);
     return;
   }
   uint64_t* full_bar = bars;                           // [STAGES]  used in the leader
@@ -1314,8 +1201,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     if (COMM == kCommAllGather && a.a_spread && lane == 0) go_ok = wait_go(a.comm) ? 1 : 0;
     go_ok = __shfl_sync(0xffffffffu, go_ok, 0);
     if (COMM == kCommAllGather && a.a_spread && !UCCL_DBG(a, 1) && go_ok) {
-      if (a.comm.a_full_mc) comm_allgather_push_mc(a, blockIdx.x, gridDim.x, lane);
-      else if (lane == 0) comm_allgather_push<FWD_SLOT_BYTES, FWD_SLOTS, 2, 2>(a, smem + PIPE_BYTES, bars + 24, blockIdx.x, gridDim.x);
+      if (lane == 0) comm_allgather_push<FWD_SLOT_BYTES, FWD_SLOTS, 2, 2>(a, smem + PIPE_BYTES, bars + 24, blockIdx.x, gridDim.x);
     }
   } else {
     // ------------------------------------------------------------ epilogue warps (both CTAs)
@@ -1323,9 +1209,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     uint8_t* stage = smem + EPI_OFF + q * NBUF * EPI_BUF_BYTES;
     uint32_t tcount = 0, stage_it = 0;
     int prev_mb = 0;
-    if (COMM == kCommReduceScatter || COMM == kCommReduceScatterCe) {
-      // no tile leaves for a peer, and no flag is raised for a copy engine, before every rank has
-      // entered this launch
+    if (COMM == kCommReduceScatter) {
+      // no tile leaves for a peer before every rank has entered this launch
       int g = 1;
       if (lane == 0) g = wait_go(a.comm) ? 1 : 0;
       if (!__shfl_sync(0xffffffffu, g, 0) && lane == 0) *bail = 1;
@@ -1339,44 +1224,11 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       if (!ptx::mbar_wait_bounded(&tfull_bar[acc], acc_ph, bail)) break;
       ptx::tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
-      if (COMM == kCommReduceScatterCe) {
-        // my own rows go straight into slot [me] of my staging buffer, the others into the send buffer
-        const int rpr = a.comm.rows_per_rank, me = a.comm.rank;
-        const int owner = min((mb * BM) / rpr, a.comm.nranks - 1);
-        __nv_bfloat16* cb = a.C;
-        if (owner == me)
-          cb = reinterpret_cast<__nv_bfloat16*>(const_cast<char*>(a.comm.stage_local) +
-                                                static_cast<size_t>(me) * rpr * a.N * 2) - static_cast<size_t>(me) * rpr * a.ldc;
-        // through TMA: the own rows go through the map of this rank's staging buffer (slot [me] holds
-        // them at their global row index), the others through the map of the send buffer
-        const CUtensorMap* cm = a.epi_tma ? (owner == me ? &pm.m[0] : &pm.m[kMaxPeers]) : nullptr;
-        epilogue_tile<EPI, kCommNone, NBUF>(a, pm, taddr, mb, nb, q, lane, stage, stage_it, cb, cm, mb * BM + q * 32);
-      } else {
-        epilogue_tile<EPI, COMM, NBUF>(a, pm, taddr, mb, nb, q, lane, stage, stage_it, a.C,
-                                       a.epi_tma ? &pm.m[kMaxPeers] : nullptr, mb * BM + q * 32);
-      }
+      epilogue_tile<EPI, COMM, NBUF>(a, pm, taddr, mb, nb, q, lane, stage, stage_it, a.C,
+                                     a.epi_tma ? &pm.m[kMaxPeers] : nullptr, mb * BM + q * 32);
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive_cluster(tempty0 + acc * 8);
-      if (COMM == kCommReduceScatterCe && lane == 0) {
-        if (a.epi_tma) ptx::tma_store_wait<0>();  // the tile's TMA stores have landed
-        // this warp's rows of the tile are written: count them for the chunk (or own row block)
-        const int rpr = a.comm.rows_per_rank, me = a.comm.rank, n = a.comm.nranks, bpr = a.m_bpr;
-        const int owner = min((mb * BM) / rpr, n - 1);
-        __threadfence();
-        if (owner == me) {
-          ptx::red_release_sys_add_u32(a.comm.done_peer[me] + static_cast<size_t>(mb) * FLAG_STRIDE, 1u);
-        } else {
-          const int qq = (owner - me - 1 + n) % n;  // position of the slab in my schedule
-          const int j = mb - owner * bpr;
-          const int idx = qq * a.comm.ce_chunks + j / (bpr / a.comm.ce_chunks);
-          const uint32_t old = atomicAdd(a.comm.slab_count + idx, 1u);
-          if (old + 1 == a.comm.slab_target) {
-            __threadfence_system();
-            asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(a.comm.slab_flag + idx), "l"(1ull) : "memory");
-          }
-        }
-      }
       if (COMM == kCommReduceScatter) {
         if (tcount > 0) publish_tile<BN / 64>(a, prev_mb, lane, &warps_done[(tcount - 1) & 3]);
         prev_mb = mb;
@@ -1395,9 +1247,9 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   }
   if (threadIdx.x == 0 && *bail && a.err) atomicCAS(a.err, 0u, 0x47454d32u);
   if (UCCL_TIMES(a) && cta_id == 0 && threadIdx.x == 0) a.times[1] = ptx::globaltimer_ns();
-  if ((COMM == kCommReduceScatter || COMM == kCommReduceScatterCe) && !*bail && !UCCL_DBG(a, 1)) {
-    if (COMM == kCommReduceScatter && UCCL_DBG(a, 128)) reduce_scatter_tail_direct(a, cta_id, a.gemm_ctas);
-    else reduce_scatter_tail(a, smem, bars + 24, bail, cta_id, a.gemm_ctas, COMM == kCommReduceScatterCe);
+  if (COMM == kCommReduceScatter && !*bail && !UCCL_DBG(a, 1)) {
+    if (UCCL_DBG(a, 128)) reduce_scatter_tail_direct(a, cta_id, a.gemm_ctas);
+    else reduce_scatter_tail(a, smem, bars + 24, bail, cta_id, a.gemm_ctas);
   }
 }
 

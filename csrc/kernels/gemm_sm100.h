@@ -41,7 +41,6 @@ struct GemmFusion {
   int a_peer_major = 0;  // visit the other ranks' shards one rank after the other, nearest first (copy-engine lanes)
   int a_spread = 0;    // no communication CTAs either: a forwarder warp in every GEMM CTA pushes the shard
   void* a_full_peer[UCCL_MAX_LOCAL_RANKS] = {};
-  void* a_full_mc = nullptr;  // multicast alias of A_full: the forwarder warps store through the switch
   uint32_t* ready_peer[UCCL_MAX_LOCAL_RANKS] = {};
   // reduce-scatter: every rank's staging buffer [nranks][rows_per_rank][N] (peer-mapped) and
   // per-row-block counters (zeroed before the launch); output of this rank
@@ -53,21 +52,10 @@ struct GemmFusion {
   // (0 = every CTA computes first and sums afterwards); tail_next: local word, zero at launch
   int rs_reducers = 0;
   uint32_t* tail_next = nullptr;
-  // role 3 (reduce-scatter by copy engines): GemmLaunch.C is the local send buffer [M, N]; the
-  // chunks of a slab are counted and flagged here, arrivals from the other ranks are flagged in ce_done
-  uint32_t* slab_count = nullptr;
-  unsigned long long* slab_flag = nullptr;
-  const uint32_t* ce_done = nullptr;
-  int ce_chunks = 0;
 };
 
 ucclResult_t launchGemmBf16(const GemmLaunch& g, const GemmFusion* fusion, cudaStream_t stream);
 
-// Loads every GEMM kernel variant on the current device (once per thread and device).  CUDA loads
-// kernels lazily, and loading one may wait for the device to go idle: a caller that is about to
-// park side streams on stream memory operations that only the GEMM kernel can satisfy must have
-// the kernel loaded first, or the load would wait for those streams for ever.
-ucclResult_t preloadGemmKernels();
 
 // Number of SMs of the current device (cached per device).
 int deviceSmCount();

@@ -2,8 +2,11 @@
 // arena and bumps a tail counter there; the receiver drains the slots into the user's buffer and
 // bumps a head counter in the sender's arena.  One launch carries a whole group of operations;
 // operations with the same peer and direction share a FIFO and run one after the other as a
-// chain, different chains run side by side.  Every chain is striped over kP2pStripes CTAs, each with its own slice of the slots and its
-// own pair of counters, so eight copy loops run in parallel per direction.
+// chain, different chains run side by side.  Every chain has kP2pStripes CTAs, each with its own
+// slice of the slots and its own pair of counters; an operation uses p2pStripesFor(bytes) of them
+// (one per 32 KiB), so up to 32 copy loops run in parallel per direction: one CTA moves only about
+// 7 GB/s through its FIFO (copy, system-scope fence, flag, per 128 KiB slot), measured 57 GB/s for
+// a 1 GiB message with eight.
 //
 // The reference lists send/recv as future work (desgin/design-spec.md:1760); its P2P transport
 // stub copies into a local staging buffer that no peer ever opens (src/transport/p2p.cc:107-151).
@@ -24,7 +27,10 @@ __device__ __forceinline__ char* slot_of(const DevComm& dc, int receiver, int se
          static_cast<size_t>(stripe) * kStripeSlotBytes;
 }
 
-__global__ void __launch_bounds__(kThreads, 1) p2p_kernel(const __grid_constant__ P2pArgs a) {
+// 256 threads and at least four CTAs per SM: every CTA of a launch that has work must be resident,
+// because it waits for its counterpart on the peer, which waits for this rank's other CTAs in turn
+constexpr int kP2pThreads = 256;
+__global__ void __launch_bounds__(kP2pThreads, 4) p2p_kernel(const __grid_constant__ P2pArgs a) {
   const DevComm& dc = a.dc;
   const int chain = blockIdx.x / kP2pStripes, stripe = blockIdx.x % kP2pStripes;
   if (chain >= a.nchains) return;
@@ -38,14 +44,16 @@ __global__ void __launch_bounds__(kThreads, 1) p2p_kernel(const __grid_constant_
   uint64_t pos = isSend ? mine->sent : mine->rcvd;
   for (int oi = first; oi >= 0; oi = a.ops[oi].next) {
     const P2pOp& op = a.ops[oi];
+    const int stripes = p2pStripesFor(op.bytes);
+    if (stripe >= stripes) continue;  // this operation is too small to need this CTA
     // stripe split in 16-byte units; the last stripe carries the byte tail
     size_t off, len;
     {
       size_t o, l;
-      split(op.bytes >> 4, kP2pStripes, stripe, &o, &l);
+      split(op.bytes >> 4, stripes, stripe, &o, &l);
       off = o << 4;
       len = l << 4;
-      if (stripe == kP2pStripes - 1) len += op.bytes & 15;
+      if (stripe == stripes - 1) len += op.bytes & 15;
     }
     for (size_t done = 0; done < len; done += kStripeSlotBytes) {
       const size_t n = min(kStripeSlotBytes, len - done);
@@ -86,7 +94,20 @@ __global__ void __launch_bounds__(kThreads, 1) p2p_kernel(const __grid_constant_
 
 cudaError_t launchP2pKernel(const P2pArgs& a, cudaStream_t stream) {
   if (a.nchains < 1 || a.nchains > kMaxP2pChains) return cudaErrorInvalidValue;
-  dev::p2p_kernel<<<a.nchains * kP2pStripes, dev::kThreads, 0, stream>>>(a);
+  // the whole grid must fit the device at once (see kP2pThreads)
+  static thread_local int capDev = -1, capacity = 0;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev != capDev) {
+    int perSm = 0, sms = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSm, dev::p2p_kernel, dev::kP2pThreads, 0) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+      return cudaGetLastError();
+    capacity = perSm * sms;
+    capDev = dev;
+  }
+  if (a.nchains * kP2pStripes > capacity) return cudaErrorLaunchOutOfResources;
+  dev::p2p_kernel<<<a.nchains * kP2pStripes, dev::kP2pThreads, 0, stream>>>(a);
   return cudaGetLastError();
 }
 

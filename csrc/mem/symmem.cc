@@ -296,6 +296,11 @@ SymSegment* SymHeap::find(const void* ptr, size_t bytes) {
   return nullptr;
 }
 
+std::vector<SymSegment*> SymHeap::segments() {
+  std::lock_guard<std::mutex> lk(mu_);
+  return segs_;
+}
+
 ucclResult_t SymHeap::release(SymSegment* seg) {
   if (!seg) return ucclInvalidArgument;
   {

@@ -28,6 +28,8 @@ struct SymSegment {
   char* local = nullptr;
   size_t size = 0;     // bytes the caller asked for
   size_t mapSize = 0;  // bytes actually mapped (granularity multiple)
+  size_t guard = 0;    // canary bytes in front of the caller's pointer (0 = no canaries), see ucclMemCheck
+  size_t userSize = 0; // bytes between the two canaries
   char* peer[UCCL_MAX_LOCAL_RANKS] = {};
   char* mc = nullptr;  // multicast alias or nullptr
   int mode = SYM_NONE;
@@ -48,6 +50,7 @@ class SymHeap {
   void releaseAll();
   // Segment that contains [ptr, ptr + bytes), or nullptr.
   SymSegment* find(const void* ptr, size_t bytes);
+  std::vector<SymSegment*> segments();  // snapshot of the live segments
 
   int mode() const { return mode_; }
   bool nvls() const { return nvls_; }

@@ -185,6 +185,7 @@ PYBIND11_MODULE(_uccl_bindings, m) {
     return reinterpret_cast<uintptr_t>(p);
   }, nogil());
   m.def("mem_free", [](uintptr_t c, uintptr_t p) { check(ucclMemFree(P(p), C(c)), "ucclMemFree", C(c)); }, nogil());
+  m.def("mem_check", [](uintptr_t c) { check(ucclMemCheck(C(c)), "ucclMemCheck", C(c)); }, nogil());
   m.def("mem_peer_pointer", [](uintptr_t c, uintptr_t p, int peer) {
     void* out = nullptr;
     check(ucclMemPeerPointer(P(p), peer, C(c), &out), "ucclMemPeerPointer", C(c));
@@ -229,9 +230,6 @@ PYBIND11_MODULE(_uccl_bindings, m) {
   });
 
   m.def("set_blocks", [](uintptr_t c, int blocks) { check(ucclCommSetBlocks(C(c), blocks), "ucclCommSetBlocks"); });
-  m.def("set_fused_rs_options", [](uintptr_t c, int rsMode, int ceChunks) {
-    check(ucclCommSetFusedRsOptions(C(c), rsMode, ceChunks), "ucclCommSetFusedRsOptions");
-  });
   m.def("set_fused_rs_reducers", [](uintptr_t c, int n) { check(ucclCommSetFusedRsReducers(C(c), n), "ucclCommSetFusedRsReducers"); });
   m.def("set_fused_options", [](uintptr_t c, int agMode, int commCtas, int ceChunks) {
     check(ucclCommSetFusedOptions(C(c), agMode, commCtas, ceChunks), "ucclCommSetFusedOptions");

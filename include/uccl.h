@@ -189,6 +189,11 @@ ucclResult_t ucclCommGetAsyncError(ucclComm_t comm, ucclResult_t* asyncError);
  * object when the hardware offers one.  Collectives on such buffers run zero-copy. */
 ucclResult_t ucclMemAlloc(void** ptr, size_t size, ucclComm_t comm);
 ucclResult_t ucclMemFree(void* ptr, ucclComm_t comm);
+/* Collective.  With UCCL_CANARY=1 every buffer of ucclMemAlloc sits between painted guard regions;
+ * this call synchronises the device and the ranks and verifies them all (ucclInternalError and a
+ * message with the buffer and the byte offset when one was overwritten).  ucclMemFree checks the
+ * buffer it releases the same way.  Without UCCL_CANARY it returns ucclSuccess. */
+ucclResult_t ucclMemCheck(ucclComm_t comm);
 /* Peer-mapped alias of a symmetric pointer (NULL result if `ptr` is not symmetric). */
 ucclResult_t ucclMemPeerPointer(const void* ptr, int peer, ucclComm_t comm, void** peerPtr);
 /* Multicast alias of a symmetric pointer (NULL result without NVLS). */
@@ -301,14 +306,9 @@ ucclResult_t ucclCommSetBlocks(ucclComm_t comm, int blocks);
  * per peer, k = k streams that serve the peers one after the other, nearest first).
  * ceChunks: copies per peer (mode 1).
  * The environment variables UCCL_FUSED_AG / UCCL_FUSED_COMM_CTAS / UCCL_FUSED_CE_CHUNKS win. */
-/* With agMode 1, commCtas = 32 + k selects k lanes plus a separate stream for the arrival flags. */
 ucclResult_t ucclCommSetFusedOptions(ucclComm_t comm, int agMode, int commCtas, int ceChunks);
-/* Options of the fused GEMM -> reduce-scatter; 0 keeps a default.  rsMode: 1 = the epilogue TMA-stores
- * every tile into the owner's memory, 2 = tiles stay local and copy engines carry each finished
- * chunk of a rank's rows to its owner (ceChunks chunks per rank, at most 8).  UCCL_FUSED_RS=kernel|ce
- * and UCCL_FUSED_RS_CHUNKS win. */
-ucclResult_t ucclCommSetFusedRsOptions(ucclComm_t comm, int rsMode, int ceChunks);
-/* CTAs of the fused GEMM -> reduce-scatter launch that do nothing but sum the staged partial tiles of
+/* The fused GEMM -> reduce-scatter has one transport: the epilogue TMA-stores every tile into the
+ * owner's memory.  Its option: CTAs of the launch that do nothing but sum the staged partial tiles of
  * this rank's rows while the others compute (0 = none: every CTA computes, then sums; at most 64).
  * Worth it where the links rather than the tensor cores set the pace.  UCCL_FUSED_RS_REDUCERS wins. */
 ucclResult_t ucclCommSetFusedRsReducers(ucclComm_t comm, int reducerCtas);

@@ -15,6 +15,13 @@
  *
  * Obtain a descriptor on the host with ucclWindowGetDeviceHandle() / ucclWindowGetDeviceHandleDyn(),
  * or assemble one from raw tables with makeDeviceWindow() (rma_device.hpp:365).
+ *
+ * Checked build: compile the including file with -DUCCL_DEVICE_CHECKS and every put / get /
+ * get-reduce / signal first tests its peer index and byte range against the descriptor
+ * (peer < nRanks, offset + bytes <= size).  An access that fails the test is left out and
+ * recorded (first one wins: kind, peer, offset, bytes) in a device variable of the including
+ * translation unit, which ucclDeviceCheckRead() copies to the host.  The reference has no bounds
+ * checks on this path (rma_device.hpp:86-127 index remotePtrs[peer] + offset directly).
  */
 #ifndef UCCL_DEVICE_CUH_
 #define UCCL_DEVICE_CUH_
@@ -101,6 +108,27 @@ __device__ __forceinline__ unsigned long long signal_load(const unsigned long lo
   return v;
 }
 
+#ifdef UCCL_DEVICE_CHECKS
+/* [0] = number of refused accesses, [1] = kind (1 put, 2 get, 3 get-reduce, 4 signal) << 32 | peer,
+ * [2] = byte offset, [3] = bytes of the first refused access */
+static __device__ unsigned long long g_check_record[4];
+template <typename W>
+__device__ __forceinline__ bool access_ok(const W& w, int kind, int peer, size_t off, size_t bytes) {
+  if (peer >= 0 && peer < w.nRanks && off <= w.size && bytes <= w.size - off) return true;
+  if (blockIdx.x == 0 && threadIdx.x == 0) {  /* the grid makes the call together: one record per call */
+    if (atomicAdd(&g_check_record[0], 1ull) == 0ull) {
+      g_check_record[1] = (static_cast<unsigned long long>(kind) << 32) | static_cast<unsigned int>(peer);
+      g_check_record[2] = off;
+      g_check_record[3] = bytes;
+    }
+  }
+  return false;
+}
+#define UCCL_DEVICE_ACCESS_OK(w, kind, peer, off, bytes) uccl_device::access_ok(w, kind, peer, off, bytes)
+#else
+#define UCCL_DEVICE_ACCESS_OK(w, kind, peer, off, bytes) true
+#endif
+
 /* grid-stride byte copy; 16-byte vectors when both sides allow it */
 __device__ __forceinline__ void copy_bytes(char* dst, const char* src, size_t bytes) {
   const size_t tid = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -142,6 +170,7 @@ struct ucclDeviceMin {
 /* The whole grid takes part: every thread copies its share.  */
 template <typename W>
 __device__ __forceinline__ void devicePut(const W& w, int peer, size_t peerOffset, const void* local, size_t bytes) {
+  if (!UCCL_DEVICE_ACCESS_OK(w, 1, peer, peerOffset, bytes)) return;
   uccl_device::copy_bytes(w.remotePtrs[peer] + peerOffset, static_cast<const char*>(local), bytes);
 }
 template <typename T, typename W>
@@ -151,6 +180,7 @@ __device__ __forceinline__ void devicePutElements(const W& w, int peer, size_t p
 }
 template <typename W>
 __device__ __forceinline__ void deviceGet(const W& w, int peer, size_t peerOffset, void* local, size_t bytes) {
+  if (!UCCL_DEVICE_ACCESS_OK(w, 2, peer, peerOffset, bytes)) return;
   uccl_device::copy_bytes(static_cast<char*>(local), w.remotePtrs[peer] + peerOffset, bytes);
 }
 template <typename T, typename W>
@@ -162,6 +192,7 @@ __device__ __forceinline__ void deviceGetElements(const W& w, int peer, size_t p
 /* Raise the counter that `peer` keeps for this rank.  Call from ONE thread. */
 template <typename W>
 __device__ __forceinline__ void deviceSignal(const W& w, int peer) {
+  if (!UCCL_DEVICE_ACCESS_OK(w, 4, peer, 0, 0)) return;
   uccl_device::signal_add(w.remoteSignals[peer] + w.myRank, 1ull);
 }
 /* Put, then signal once the whole CTA's part has been written.  All threads of the CTA call;
@@ -170,14 +201,16 @@ __device__ __forceinline__ void deviceSignal(const W& w, int peer) {
 template <typename W>
 __device__ __forceinline__ void devicePutSignal(const W& w, int peer, size_t peerOffset, const void* local,
                                                 size_t bytes) {
-  devicePut(w, peer, peerOffset, local, bytes);
+  if (!UCCL_DEVICE_ACCESS_OK(w, 1, peer, peerOffset, bytes)) return;  /* no signal for data that was not written */
+  uccl_device::copy_bytes(w.remotePtrs[peer] + peerOffset, static_cast<const char*>(local), bytes);
   __syncthreads();
-  if (threadIdx.x == 0) deviceSignal(w, peer);
+  if (threadIdx.x == 0) uccl_device::signal_add(w.remoteSignals[peer] + w.myRank, 1ull);
 }
 /* Get, then bump the local counter of `peer` (completion marker for this rank's own waits). */
 template <typename W>
 __device__ __forceinline__ void deviceGetSignal(const W& w, int peer, size_t peerOffset, void* local, size_t bytes) {
-  deviceGet(w, peer, peerOffset, local, bytes);
+  if (!UCCL_DEVICE_ACCESS_OK(w, 2, peer, peerOffset, bytes)) return;
+  uccl_device::copy_bytes(static_cast<char*>(local), w.remotePtrs[peer] + peerOffset, bytes);
   __syncthreads();
   if (threadIdx.x == 0) uccl_device::signal_add(w.localSignals + peer, 1ull);
 }
@@ -223,6 +256,7 @@ __device__ __forceinline__ bool deviceWaitSignalMulti(const W& w, const int* pee
 template <typename T, typename RedOp, typename W>
 __device__ __forceinline__ void deviceGetReduce(const W& w, const T* local, T* result, size_t count, int peer,
                                                 size_t peerByteOffset) {
+  if (!UCCL_DEVICE_ACCESS_OK(w, 3, peer, peerByteOffset, count * sizeof(T))) return;
   const T* remote = reinterpret_cast<const T*>(w.remotePtrs[peer] + peerByteOffset);
   RedOp op;
   const size_t tid = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -236,6 +270,16 @@ __device__ __forceinline__ void deviceGetReduceF32(const W& w, int peer, size_t 
                                                    size_t count) {
   deviceGetReduce<float, ucclDeviceSum>(w, local, local, count, peer, peerElemOffset * sizeof(float));
 }
+
+#ifdef UCCL_DEVICE_CHECKS
+/* Host: copies the record of refused accesses (see the top of this file) into out[4] and clears it. */
+static inline cudaError_t ucclDeviceCheckRead(unsigned long long out[4]) {
+  cudaError_t e = cudaMemcpyFromSymbol(out, uccl_device::g_check_record, 4 * sizeof(unsigned long long));
+  if (e != cudaSuccess) return e;
+  const unsigned long long zero[4] = {0, 0, 0, 0};
+  return cudaMemcpyToSymbol(uccl_device::g_check_record, zero, sizeof(zero));
+}
+#endif
 
 #endif /* __CUDACC__ */
 #endif /* UCCL_DEVICE_CUH_ */

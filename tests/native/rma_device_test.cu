@@ -4,6 +4,10 @@
 //
 // The reference declares the same calls as SYCL inlines (src/rma/rma_device.hpp:84-357) and has
 // no test for them.
+//
+// Compiled with the header's checked mode on: every access of the tests below passes through the
+// bounds test, and ucclDevTestCheckRead returns the record of the ones it refused.
+#define UCCL_DEVICE_CHECKS 1
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -104,6 +108,9 @@ int waitReduce(void* win, int peer, unsigned long long expected, int dtype, cons
 }  // namespace
 
 extern "C" {
+
+// out[4]: count of refused accesses, (kind << 32 | peer), offset, bytes of the first; clears the record
+int ucclDevTestCheckRead(unsigned long long* out) { return check(ucclDeviceCheckRead(out)); }
 
 // dyn != 0 selects the pointer-table descriptor (ucclDeviceWindowDyn).
 int ucclDevTestPutSignal(void* win, int dyn, int peer, size_t peerOff, const void* local, size_t bytes, void* stream) {

@@ -385,12 +385,11 @@ def case_api_contract(comm, rank, n, args):
             pass
     comm.set_fused_options("spread")
     comm.set_fused_options()
-    comm.set_fused_rs_options("ce", 4)
-    comm.set_fused_rs_options("kernel")
-    comm.set_fused_rs_options()
-    for bad in (("ce", 9), ("ce", -1)):
+    comm.set_fused_rs_reducers(8)
+    comm.set_fused_rs_reducers(0)
+    for bad in (65, -1):
         try:
-            comm.set_fused_rs_options(*bad)
+            comm.set_fused_rs_reducers(bad)
             fail.append(("bad fused reduce-scatter option accepted", bad))
         except Exception:
             pass
@@ -439,23 +438,19 @@ def case_tp_mlp(comm, rank, n, args):
 
     dev = _dev(comm, rank)
     fail = []
-    # every way of moving the all-gather's rows: copy engines, dedicated CTAs, a forwarder warp per CTA
-    modes = [("ce", "kernel"), ("kernel", "kernel"), ("spread", "kernel")] if n > 1 else [("ce", "kernel")]
-    if n > 1:  # reduce-scatter carried by copy engines
-        modes += [("spread", "ce"), ("ce", "ce")]
-    if args:  # a subset, "ag/rs,ag/rs,..." (for bisecting a failure)
+    # every way of moving the all-gather's rows (copy engines, dedicated CTAs, a forwarder warp per CTA),
+    # and the reduce-scatter with and without CTAs that only sum: "all-gather mode/reducer CTAs"
+    modes = [("ce", "0"), ("kernel", "0"), ("spread", "0"), ("ce", "8"), ("spread", "16")] if n > 1 else [("ce", "0")]
+    if args:  # a subset, "ag/reducers,ag/reducers,..."
         modes = [tuple(m.split("/")) for m in args[0].split(",")]
-    if n > 1 and not args:
-        modes += [("ce", "kernel+reducers")]  # a few CTAs only sum while the others compute
     for ag_mode, rs_mode in modes:
         os.environ["UCCL_FUSED_AG"] = ag_mode
-        os.environ["UCCL_FUSED_RS_REDUCERS"] = "8" if rs_mode.endswith("+reducers") else "0"
-        rs_mode = rs_mode.split("+")[0]
-        os.environ["UCCL_FUSED_RS"] = rs_mode
-        shapes = [(512, 1024, 256 * n), (1024, 3584 * 2, 128 * n)]
-        if rs_mode == "ce":
-            shapes.append((512, 2048, 1024 * n))  # several chunks per rank
+        os.environ["UCCL_FUSED_RS_REDUCERS"] = rs_mode
+        shapes = [(512, 1024, 256 * n), (1024, 3584 * 2, 128 * n), (512, 2048, 1024 * n)]
         for hidden, ffn, tokens in shapes:
+            # a run that is cut off by its time limit still says how far it got
+            print("tp_mlp rank %d: all-gather %s, reducer CTAs %s, shape %s" % (rank, ag_mode, rs_mode, (hidden, ffn, tokens)),
+                  file=sys.stderr, flush=True)
             mlp = TensorParallelMLP(comm, hidden, ffn, tokens, seed=3)
             x_full = torch.randn(tokens, hidden, generator=torch.Generator().manual_seed(11)).to(torch.bfloat16).to(dev)
             rows = tokens // n
@@ -475,7 +470,6 @@ def case_tp_mlp(comm, rank, n, args):
             if not torch.equal(gathered, x_full):
                 fail.append((ag_mode, "x_full not gathered", hidden, tokens))
     os.environ.pop("UCCL_FUSED_AG", None)
-    os.environ.pop("UCCL_FUSED_RS", None)
     os.environ.pop("UCCL_FUSED_RS_REDUCERS", None)
     return {"fail": fail, "nvls": comm.info["nvls"], "async": comm.async_error(), "last": comm.last_error()}
 
@@ -639,6 +633,23 @@ def case_rma_device(comm, rank, n, args):
             z = torch.ones(8, device=dev) * 2
             if z.sum().item() != 16:
                 fail.append(("context unusable",))
+            # checked mode of the header: a put that would run 56 bytes past the window is left out and
+            # recorded; nothing in the run so far was refused
+            rec = (ctypes.c_ulonglong * 4)()
+            lib.ucclDevTestCheckRead.argtypes = [vp]
+            if lib.ucclDevTestCheckRead(ctypes.cast(rec, vp)) != 0 or rec[0] != 0:
+                fail.append(("check record not clean", list(rec)))
+            barrier()
+            before = buf.clone()
+            src = torch.full((16,), 7.0, device=dev)
+            rc = lib.ucclDevTestPutSignal(win._win, 0, nxt, cnt * 4 - 8, src.data_ptr(), 64, stream)
+            _sync(comm)
+            barrier()
+            lib.ucclDevTestCheckRead(ctypes.cast(rec, vp))
+            if rc != 0 or rec[0] != 1 or rec[1] != ((1 << 32) | nxt) or rec[2] != cnt * 4 - 8 or rec[3] != 64:
+                fail.append(("out-of-window put not refused", rc, list(rec)))
+            if not torch.equal(before, buf):
+                fail.append(("out-of-window put touched the window",))
         barrier()
         win.close()
         comm.free(buf)
@@ -703,6 +714,47 @@ def case_moe(comm, rank, n, args):
             fail.append(("overflow", hidden))
         disp.close()
     return {"fail": fail}
+
+
+def case_canary(comm, rank, n, args):
+    """UCCL_CANARY=1: collectives on odd-sized symmetric buffers leave the guard regions intact; a store
+    just past a buffer's end (inside this rank's own mapping, so nothing faults) is found and located."""
+    from unified_ccl_b200.communicator import _tensor_from_ptr
+    dev = _dev(comm, rank)
+    fail = []
+    numel = 70001  # not a multiple of a 16-byte vector
+    x = comm.empty((numel,), torch.bfloat16)
+    g = comm.empty((numel * n,), torch.bfloat16)
+    for it in range(2):
+        x.copy_(torch.full((numel,), float(rank + 1), device=dev, dtype=torch.bfloat16))
+        comm.allreduce(x)
+        comm.allgather(x, g)
+        comm.reduce_scatter(g, x)
+        _sync(comm)
+    try:
+        comm.check_memory()
+    except Exception as e:  # noqa: BLE001
+        fail.append(("clean run flagged", str(e)))
+    # overrun: eight elements behind the end of x, written by this rank through its own mapping
+    over = _tensor_from_ptr(x.data_ptr(), numel + 8, torch.bfloat16, dev.index)
+    over[numel + 3 :].fill_(1.0)
+    _sync(comm)
+    msg = None
+    try:
+        comm.check_memory()
+    except Exception as e:  # noqa: BLE001
+        msg = str(e)
+    if msg is None or ("offset %d" % ((numel + 3) * 2)) not in (comm.last_error() + msg):
+        fail.append(("overrun not located", msg, comm.last_error()))
+    freed_err = None
+    try:
+        comm.free(x)
+    except Exception as e:  # noqa: BLE001
+        freed_err = str(e)
+    if freed_err is None:
+        fail.append(("free did not report the overrun",))
+    comm.free(g)
+    return {"fail": fail, "msg": msg}
 
 
 def case_skipped_collective(comm, rank, n, args):

@@ -25,6 +25,10 @@ def test_collective_matrix_symmetric_buffers():
     assert_all_ok(run_ranks("collectives_symmetric", _n(), timeout=300))
 
 
+def test_canaries_stay_intact_under_collectives():
+    assert_all_ok(run_ranks("canary", _n(), env={"UCCL_CANARY": "1"}, timeout=200))
+
+
 def test_allreduce_every_algorithm():
     res = run_ranks("allreduce_algos", _n(), timeout=400)
     assert_all_ok(res)
@@ -67,8 +71,12 @@ def test_fused_allreduce_residual_rmsnorm():
     assert_all_ok(run_ranks("fused_norm", _n()))
 
 
-def test_tensor_parallel_mlp():
-    assert_all_ok(run_ranks("tp_mlp", _n(), timeout=300))
+# all-gather transport / reducer CTAs of the reduce-scatter; each pair runs as rank processes of its own,
+# so that one pair's failure or time limit says which pair it was and leaves the others their verdict
+@pytest.mark.parametrize("modes", ["ce/0", "kernel/0", "spread/0", "ce/8", "spread/16"])
+def test_tensor_parallel_mlp(modes):
+    assert_all_ok(run_ranks("tp_mlp", _n(), timeout=120, args=[modes],
+                            env={"UCCL_WAIT_TIMEOUT_MS": "5000", "UCCL_TEST_DUMP_AFTER_S": "100"}))
 
 
 def test_moe_dispatch_combine():

@@ -33,6 +33,11 @@ def test_moe_single_rank():
 
 
 @gpu
+def test_canaries_around_symmetric_buffers():
+    assert_all_ok(run_ranks("canary", 1, env={"UCCL_CANARY": "1"}))
+
+
+@gpu
 def test_native_library_is_loaded():
     """The CUDA path must come from this repository's shared objects, not from a fallback."""
     import unified_ccl_b200 as u

@@ -8,6 +8,12 @@ with the build command in the message.
 """
 import os as _os
 
+# The copy-engine transports keep one stream per peer (plus one for flags) busy next to the caller's
+# stream, some of them parked on a memory value.  With the CUDA default of 8 hardware queues per
+# context, streams share queues and a parked one holds up whatever was queued behind it.  The
+# variable is read when the context is created, so it is set here unless the user chose a value.
+_os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "32")
+
 try:
     from . import _uccl_bindings as _C  # noqa: F401
 except ImportError as _e:  # pragma: no cover - exercised only on a broken checkout

@@ -294,6 +294,13 @@ class Communicator:
             _C.mem_free(self._comm, ptr)
             del self._sym[ptr]
 
+    def check_memory(self):
+        """Collective: verify the guard regions around every symmetric buffer (needs ``UCCL_CANARY=1`` in
+        the environment when the communicator is created; a no-op otherwise).  Raises when a store
+        landed outside a buffer; the message names the buffer and the byte offset."""
+        if self.on_gpu:
+            _C.mem_check(self._comm)
+
     def is_symmetric(self, tensor: torch.Tensor) -> bool:
         return _C.mem_peer_pointer(self._comm, tensor.data_ptr(), self._rank) != 0 if self.on_gpu else False
 
@@ -308,16 +315,9 @@ class Communicator:
     def set_fused_options(self, ag_mode: str = "auto", comm_ctas: int = 0, ce_chunks: int = 0):
         """How the all-gather -> GEMM fusion moves its rows: ``"ce"`` (copy engines, ``ce_chunks`` copies per
         peer; ``comm_ctas`` then is the number of copy-engine lanes, 0 = one stream per peer, k = k streams
-        that serve the peers one after the other, 32 + k = k streams plus one more stream that carries the
-        arrival flags so that the data copies run back to back), ``"kernel"`` (``comm_ctas`` communication CTAs inside the
+        that serve the peers one after the other), ``"kernel"`` (``comm_ctas`` communication CTAs inside the
         GEMM launch) or ``"spread"`` (a forwarder warp in every GEMM CTA); 0 keeps a default."""
         _C.set_fused_options(self._comm, {"auto": 0, "ce": 1, "kernel": 2, "spread": 3}[ag_mode], int(comm_ctas), int(ce_chunks))
-
-    def set_fused_rs_options(self, rs_mode: str = "auto", ce_chunks: int = 0):
-        """How the GEMM -> reduce-scatter fusion moves its tiles: ``"kernel"`` (the epilogue TMA-stores every
-        tile into the owner's memory) or ``"ce"`` (tiles stay local, copy engines carry each finished chunk
-        of a rank's rows to its owner, ``ce_chunks`` chunks per rank)."""
-        _C.set_fused_rs_options(self._comm, {"auto": 0, "kernel": 1, "ce": 2}[rs_mode], int(ce_chunks))
 
     def set_fused_rs_reducers(self, reducer_ctas: int = 0):
         """CTAs of the fused GEMM -> reduce-scatter launch that only sum the staged partial tiles (0 = none)."""

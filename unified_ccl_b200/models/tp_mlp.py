@@ -48,20 +48,11 @@ class TensorParallelMLP:
     __call__ = forward
 
     # candidates of autotune(): (all-gather mode, communication CTAs or copy-engine lanes, chunks per peer)
-    # "spread" stores through the switch where the buffer has a multicast alias and there are more than two
-    # ranks; "spread_uc" is the same forwarder warp with unicast bulk copies
     # "ce" with 32 + k communication CTAs: k copy-engine lanes and a stream of its own for the arrival flags
-    AG_CANDIDATES = (("ce", 0, 2), ("ce", 1, 2), ("ce", 1, 4), ("ce", 33, 1), ("ce", 33, 2), ("ce", 33, 4), ("ce", 34, 2),
-                     ("spread", 0, 0), ("spread_uc", 0, 0), ("kernel", 4, 0), ("kernel", 8, 0), ("kernel", 16, 0))
+    AG_CANDIDATES = (("ce", 0, 2), ("ce", 1, 2), ("ce", 1, 4), ("ce", 33, 2),
+                     ("spread", 0, 0), ("kernel", 8, 0), ("kernel", 16, 0))
 
     def _apply_ag(self, mode, ctas, chunks):
-        import os
-
-        if mode == "spread_uc":
-            os.environ["UCCL_FUSED_AG_MC"] = "0"
-            mode = "spread"
-        else:
-            os.environ.pop("UCCL_FUSED_AG_MC", None)
         self.comm.set_fused_options(mode, ctas, chunks)
 
     def autotune(self, x_shard: torch.Tensor, iters: int = 3, candidates=None):
@@ -98,17 +89,11 @@ class TensorParallelMLP:
         self.ag_choice = cands[best]
         return {cands[i]: round(avg[i], 1) for i in range(len(cands))}
 
-    # candidates of autotune_rs(): (reduce-scatter mode, copy-engine chunks per rank)
-    # (mode, copy-engine chunks per rank | for "kernel": CTAs that only sum)
-    RS_CANDIDATES = (("kernel", 0), ("kernel", 8), ("kernel", 16), ("kernel", 24), ("ce", 1), ("ce", 2))
+    # candidates of autotune_rs(): ("kernel", CTAs that only sum)
+    RS_CANDIDATES = (("kernel", 0), ("kernel", 8), ("kernel", 16), ("kernel", 24))
 
     def _apply_rs(self, mode, arg):
-        if mode == "kernel":
-            self.comm.set_fused_rs_options("kernel", 0)
-            self.comm.set_fused_rs_reducers(arg)
-        else:
-            self.comm.set_fused_rs_options(mode, arg)
-            self.comm.set_fused_rs_reducers(0)
+        self.comm.set_fused_rs_reducers(arg)
 
     def autotune_rs(self, iters: int = 3, candidates=None):
         """The same for the GEMM -> reduce-scatter half (``self.h`` must hold activations, e.g. after one
