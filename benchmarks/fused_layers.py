@@ -41,7 +41,7 @@ def main():
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
     from unified_ccl_b200 import Communicator, Window
-    from unified_ccl_b200.parallel import MoeDispatcher, allreduce_residual_rmsnorm
+    from unified_ccl_b200.parallel import MoeDispatcher, allreduce_residual_rmsnorm, autotune_allreduce_residual_rmsnorm
 
     comm = Communicator(rank, world)
     n = world
@@ -85,6 +85,8 @@ def main():
             rn.copy_(h)
             return torch.nn.functional.rms_norm(h, (H,), gamma, 1e-6)
 
+        # untimed: pick the shape of the kernel's switch path on this box (same on every rank)
+        shapes = autotune_allreduce_residual_rmsnorm(comm, x, res, gamma, 1e-6, out=out)
         us_f = timed(lambda: allreduce_residual_rmsnorm(comm, x, res, gamma, 1e-6, out=out, residual_out=res))
         us_b = timed(baseline)
         msg = T * H * 2
@@ -92,7 +94,8 @@ def main():
         roof_nvls = max(msg / 770e9, 4 * msg / 6549e9) * 1e6
         emit({"bench": "allreduce_residual_rmsnorm", "n": n, "tokens": T, "hidden": H, "fused_us": round(us_f, 1),
               "nccl_plus_norm_us": round(us_b, 1), "speedup": round(us_b / us_f, 3), "roofline_ring_us": round(roof, 1),
-              "roofline_switch_us": round(roof_nvls, 1), "frac_of_ring_roofline": round(roof / us_f, 3), "nvls": comm.info["nvls"]})
+              "roofline_switch_us": round(roof_nvls, 1), "frac_of_ring_roofline": round(roof / us_f, 3), "nvls": comm.info["nvls"],
+              "autotune_rows_us": {str(k): v for k, v in shapes.items()}})
         if "norm_breakdown" in what and n > 1:
             # the same kernel with a phase left out (UCCL_NORM_DEBUG), and the two data paths
             parts = {}

@@ -101,6 +101,7 @@ struct Comm {
   cudaEvent_t ceStart = nullptr;
   bool ceReady = false;
   int fusedRsReducers = 0;                  // ucclCommSetFusedRsReducers: CTAs that only sum
+  int fusedNormRows = -1;                   // ucclCommSetFusedNormRows: rows per pass of the fused norm's all-reduce phase (-1 = default)
   void* onesDev = nullptr;            // 32-bit ones at the GEMM flag stride (source of copy-engine flag writes)
 
   // network path

@@ -137,7 +137,8 @@ extern "C" ucclResult_t ucclAllReduceResidualRMSNorm(const void* x, const void* 
     a.debug = dbg ? atoi(dbg) : 0;
   }
 #endif
-  a.mcRows = 4;  // rows per pass of the all-reduce phase on the switch path; 0 = normalise own rows from registers
+  // rows per pass of the all-reduce phase on the switch path; 0 = normalise own rows from registers
+  a.mcRows = c->fusedNormRows >= 0 ? c->fusedNormRows : 4;
   if (const char* e = getenv("UCCL_NORM_MC_ROWS")) a.mcRows = atoi(e);
   if (a.mcRows < 0 || a.mcRows > 4) a.mcRows = 4;
   commCount(c, ucclCollAllReduce, bytes, c->arena && c->arena->mc ? ucclAlgoNvls : ucclAlgoTwoShot);

@@ -616,6 +616,13 @@ extern "C" ucclResult_t ucclCommSetFusedRsReducers(ucclComm_t comm, int reducerC
   return ucclSuccess;
 }
 
+extern "C" ucclResult_t ucclCommSetFusedNormRows(ucclComm_t comm, int rows) {
+  Comm* c = toComm(comm);
+  if (!commValid(c) || rows < -1 || rows > 4) return ucclInvalidArgument;
+  c->fusedNormRows = rows;
+  return ucclSuccess;
+}
+
 extern "C" ucclResult_t ucclCommSetBlocks(ucclComm_t comm, int blocks) {
   Comm* c = toComm(comm);
   if (!commValid(c) || blocks < 0 || blocks > kMaxBlocks) return ucclInvalidArgument;

@@ -230,6 +230,7 @@ PYBIND11_MODULE(_uccl_bindings, m) {
   });
 
   m.def("set_blocks", [](uintptr_t c, int blocks) { check(ucclCommSetBlocks(C(c), blocks), "ucclCommSetBlocks"); });
+  m.def("set_fused_norm_rows", [](uintptr_t c, int rows) { check(ucclCommSetFusedNormRows(C(c), rows), "ucclCommSetFusedNormRows"); });
   m.def("set_fused_rs_reducers", [](uintptr_t c, int n) { check(ucclCommSetFusedRsReducers(C(c), n), "ucclCommSetFusedRsReducers"); });
   m.def("set_fused_options", [](uintptr_t c, int agMode, int commCtas, int ceChunks) {
     check(ucclCommSetFusedOptions(C(c), agMode, commCtas, ceChunks), "ucclCommSetFusedOptions");

@@ -312,6 +312,11 @@ ucclResult_t ucclCommSetFusedOptions(ucclComm_t comm, int agMode, int commCtas, 
  * this rank's rows while the others compute (0 = none: every CTA computes, then sums; at most 64).
  * Worth it where the links rather than the tensor cores set the pace.  UCCL_FUSED_RS_REDUCERS wins. */
 ucclResult_t ucclCommSetFusedRsReducers(ucclComm_t comm, int reducerCtas);
+/* Fused all-reduce + residual + RMSNorm on the switch path: 1..4 = the kernel first all-reduces the rows
+ * (that many rows of every CTA per pass), then normalises all rows from local memory; 0 = one phase,
+ * every rank normalises the rows it reduced from registers and multicasts both results; -1 = default (4).
+ * UCCL_NORM_MC_ROWS wins. */
+ucclResult_t ucclCommSetFusedNormRows(ucclComm_t comm, int rows);
 
 #ifdef __cplusplus
 }

@@ -319,6 +319,11 @@ class Communicator:
         GEMM launch) or ``"spread"`` (a forwarder warp in every GEMM CTA); 0 keeps a default."""
         _C.set_fused_options(self._comm, {"auto": 0, "ce": 1, "kernel": 2, "spread": 3}[ag_mode], int(comm_ctas), int(ce_chunks))
 
+    def set_fused_norm_rows(self, rows: int = -1):
+        """Shape of the fused all-reduce + residual + RMSNorm on the switch path: 1..4 = all-reduce phase with
+        that many rows per CTA and pass, then a local normalise phase; 0 = one phase; -1 = default."""
+        _C.set_fused_norm_rows(self._comm, int(rows))
+
     def set_fused_rs_reducers(self, reducer_ctas: int = 0):
         """CTAs of the fused GEMM -> reduce-scatter launch that only sum the staged partial tiles (0 = none)."""
         _C.set_fused_rs_reducers(self._comm, int(reducer_ctas))

@@ -31,6 +31,37 @@ def allreduce_residual_rmsnorm(comm: Communicator, x: torch.Tensor, residual: to
     return out, residual_out
 
 
+def autotune_allreduce_residual_rmsnorm(comm: Communicator, x: torch.Tensor, residual: torch.Tensor, gamma: torch.Tensor,
+                                        eps: float = 1e-6, out: torch.Tensor = None, iters: int = 5, candidates=(0, 1, 2, 4)):
+    """Times :func:`allreduce_residual_rmsnorm` on these tensors under each shape of its switch path (CUDA
+    events, summed over the ranks so that every rank takes the same decision), keeps the fastest on this
+    communicator and returns ``{rows: microseconds averaged over ranks}``.  ``residual`` is used as scratch
+    output.  Collective; a no-op without an NVSwitch multicast alias or on one rank."""
+    if comm.world_size == 1 or not comm.info["nvls"]:
+        return {}
+    if out is None:
+        out = torch.empty_like(x)
+    scratch = torch.empty_like(residual)
+    stream = torch.cuda.current_stream(x.device)
+    times = torch.zeros(len(candidates), device=x.device, dtype=torch.float32)
+    for i, rows in enumerate(candidates):
+        comm.set_fused_norm_rows(rows)
+        allreduce_residual_rmsnorm(comm, x, residual, gamma, eps, out=out, residual_out=scratch)  # warm-up
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record(stream)
+        for _ in range(iters):
+            allreduce_residual_rmsnorm(comm, x, residual, gamma, eps, out=out, residual_out=scratch)
+        e.record(stream)
+        e.synchronize()
+        times[i] = s.elapsed_time(e) * 1e3 / iters
+    comm.allreduce(times)
+    stream.synchronize()
+    avg = (times / comm.world_size).tolist()
+    best = min(range(len(candidates)), key=lambda i: avg[i])
+    comm.set_fused_norm_rows(candidates[best])
+    return {candidates[i]: round(avg[i], 1) for i in range(len(candidates))}
+
+
 def allgather_gemm(comm: Communicator, x_shard: torch.Tensor, x_full: torch.Tensor, w: torch.Tensor,
                    out: torch.Tensor = None, swiglu: bool = False) -> torch.Tensor:
     """``out = allgather(x_shard) @ w.T`` with the gather overlapped tile by tile with the GEMM.
