@@ -35,6 +35,7 @@ def main():
     ap.add_argument("--dtypes", default="bf16")
     ap.add_argument("--unregistered", action="store_true", help="also time ordinary (non-symmetric) buffers")
     ap.add_argument("--blocks", default="", help="comma list of CTA counts to try besides the tuner's (two-shot / NVLS, from 256 KiB up)")
+    ap.add_argument("--auto-only", action="store_true", help="time NCCL and the tuner's own choice only (e.g. with UCCL_TUNE_FILE set to a table just measured)")
     ap.add_argument("--no-table", action="store_true", help="measure with the built-in priors (UCCL_TUNE_AUTO=0)")
     args = ap.parse_args()
 
@@ -86,6 +87,8 @@ def main():
     def record(coll, impl, algo, proto, dt, nbytes, us, busf, registered, blocks=0):
         row = {"coll": coll, "impl": impl, "algo": algo, "proto": proto, "dtype": dt, "bytes": nbytes, "us": round(us, 2),
                "busbw_gbs": round(nbytes * busf / (us * 1e-6) / 1e9, 2), "n": n, "registered": registered, "blocks": blocks}
+        if impl == "uccl" and algo == "auto" and coll != "sendrecv":
+            row["chosen"] = "%s/%s/%d" % comm.query_tuning(coll, nbytes, registered)  # what the tuner ran
         results.append(row)
         if rank == 0:
             print(json.dumps(row), flush=True)
@@ -95,6 +98,8 @@ def main():
     def uccl_algo(coll, qname, algo, proto, dtn, nbytes, fn, it, busf):
         """Time one (algorithm, protocol) at the tuner's CTA count and, from 256 KiB up, at every count of
         --blocks; every result is recorded, the tuner table keeps the best per size."""
+        if args.auto_only:
+            return
         comm.set_algo(algo, proto)
         comm.set_blocks(0)
         us = timed(fn, it)
