@@ -43,8 +43,6 @@ const DriverApi& driverApi() {
     ok &= resolve("cuMemGetAllocationGranularity", &api.memGetAllocationGranularity);
     ok &= resolve("cuDeviceGetAttribute", &api.deviceGetAttribute);
     ok &= resolve("cuDeviceGet", &api.deviceGet);
-    ok &= resolve("cuStreamWriteValue64", &api.streamWriteValue64);
-    ok &= resolve("cuStreamWaitValue64", &api.streamWaitValue64);
     ok &= resolve("cuGetErrorString", &api.getErrorString);
     ok &= resolve("cuCtxGetCurrent", &api.ctxGetCurrent);
     ok &= resolve("cuMemGetAddressRange", &api.memGetAddressRange);

@@ -28,8 +28,6 @@ struct DriverApi {
   decltype(&cuMulticastGetGranularity) multicastGetGranularity = nullptr;
   decltype(&cuDeviceGetAttribute) deviceGetAttribute = nullptr;
   decltype(&cuDeviceGet) deviceGet = nullptr;
-  decltype(&cuStreamWriteValue64) streamWriteValue64 = nullptr;
-  decltype(&cuStreamWaitValue64) streamWaitValue64 = nullptr;
   decltype(&cuGetErrorString) getErrorString = nullptr;
   decltype(&cuCtxGetCurrent) ctxGetCurrent = nullptr;
   decltype(&cuMemGetAddressRange) memGetAddressRange = nullptr;

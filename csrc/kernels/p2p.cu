@@ -4,7 +4,7 @@
 // operations with the same peer and direction share a FIFO and run one after the other as a
 // chain, different chains run side by side.  Every chain has kP2pStripes CTAs, each with its own
 // slice of the slots and its own pair of counters; an operation uses p2pStripesFor(bytes) of them
-// (one per 32 KiB), so up to 32 copy loops run in parallel per direction: one CTA moves only about
+// (one per 512 KiB), so up to 32 copy loops run in parallel per direction: one CTA moves only about
 // 7 GB/s through its FIFO (copy, system-scope fence, flag, per 128 KiB slot), measured 57 GB/s for
 // a 1 GiB message with eight.
 //
@@ -77,10 +77,10 @@ __global__ void __launch_bounds__(kP2pThreads, 4) p2p_kernel(const __grid_consta
       len = l << 4;
       if (stripe == stripes - 1) len += op.bytes & 15;
     }
-    // a stripe's share travels in at least four pieces (16 KiB or more each, at most a slot), so
+    // a stripe's share travels in at least four pieces (32 KiB or more each, at most a slot), so
     // that the receiver drains one piece while the sender fills the next
     size_t piece = ((len + 3) / 4 + 15) & ~size_t(15);
-    piece = min(kStripeSlotBytes, max(piece, static_cast<size_t>(16u << 10)));
+    piece = min(kStripeSlotBytes, max(piece, static_cast<size_t>(32u << 10)));
     for (size_t done = 0; done < len; done += piece) {
       const size_t n = min(piece, len - done);
       if (isSend) {
@@ -92,10 +92,8 @@ __global__ void __launch_bounds__(kP2pThreads, 4) p2p_kernel(const __grid_consta
         p2p_copy(slot_of(dc, peer, dc.rank, static_cast<int>(pos % kP2pSlots), stripe), op.src + off + done, n);
         __syncthreads();
         ++pos;
-        if (threadIdx.x == 0) {
-          ptx::fence_sys();
-          ptx::st_release_sys_u64(&theirs->tail, pos);
-        }
+        // the release orders the CTA's copies (which the barrier above ordered before this thread) before the flag
+        if (threadIdx.x == 0) ptx::st_release_sys_u64(&theirs->tail, pos);
       } else {
         if (threadIdx.x == 0) s_ok = wait_u64(&mine->tail, pos + 1, dc, DEV_TIMEOUT_P2P, peer, static_cast<uint32_t>(pos));
         __syncthreads();
@@ -103,10 +101,7 @@ __global__ void __launch_bounds__(kP2pThreads, 4) p2p_kernel(const __grid_consta
         p2p_copy(op.dst + off + done, slot_of(dc, dc.rank, peer, static_cast<int>(pos % kP2pSlots), stripe), n);
         __syncthreads();
         ++pos;
-        if (threadIdx.x == 0) {
-          ptx::fence_sys();
-          ptx::st_release_sys_u64(&theirs->head, pos);
-        }
+        if (threadIdx.x == 0) ptx::st_release_sys_u64(&theirs->head, pos);
       }
     }
   }

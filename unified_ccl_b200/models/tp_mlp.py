@@ -52,10 +52,17 @@ class TensorParallelMLP:
     AG_CANDIDATES = (("ce", 0, 2), ("ce", 1, 2), ("ce", 1, 4), ("ce", 33, 2),
                      ("spread", 0, 0), ("kernel", 8, 0), ("kernel", 16, 0))
 
+    def _align(self, stream):
+        """Lines the ranks' hosts up before a timed region, so that it is not spent waiting for a late peer."""
+        if not hasattr(self, "_tick"):
+            self._tick = torch.zeros(1, device=self.h.device)
+        self.comm.allreduce(self._tick)
+        stream.synchronize()
+
     def _apply_ag(self, mode, ctas, chunks):
         self.comm.set_fused_options(mode, ctas, chunks)
 
-    def autotune(self, x_shard: torch.Tensor, iters: int = 3, candidates=None):
+    def autotune(self, x_shard: torch.Tensor, iters: int = 5, candidates=None):
         """Times the all-gather -> GEMM half of the block under each candidate setting (CUDA events,
         summed over the ranks so that every rank takes the same decision) and keeps the fastest.
         Returns ``{candidate: microseconds averaged over ranks}``; a no-op on one rank."""
@@ -70,6 +77,7 @@ class TensorParallelMLP:
             try:
                 self._apply_ag(mode, ctas, chunks)
                 allgather_gemm(self.comm, x_shard, self.x_full, self.w_gate_up, out=self.h, swiglu=True)  # warm-up
+                self._align(stream)
                 s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 s.record(stream)
                 for _ in range(iters):
@@ -95,7 +103,7 @@ class TensorParallelMLP:
     def _apply_rs(self, mode, arg):
         self.comm.set_fused_rs_reducers(arg)
 
-    def autotune_rs(self, iters: int = 3, candidates=None):
+    def autotune_rs(self, iters: int = 5, candidates=None):
         """The same for the GEMM -> reduce-scatter half (``self.h`` must hold activations, e.g. after one
         forward pass)."""
         if self.tp == 1:
@@ -107,6 +115,7 @@ class TensorParallelMLP:
             try:
                 self._apply_rs(mode, chunks)
                 gemm_reduce_scatter(self.comm, self.h, self.w_down, self.c_partial, out=self.y)  # warm-up
+                self._align(stream)
                 s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 s.record(stream)
                 for _ in range(iters):

@@ -32,25 +32,29 @@ def allreduce_residual_rmsnorm(comm: Communicator, x: torch.Tensor, residual: to
 
 
 def autotune_allreduce_residual_rmsnorm(comm: Communicator, x: torch.Tensor, residual: torch.Tensor, gamma: torch.Tensor,
-                                        eps: float = 1e-6, out: torch.Tensor = None, iters: int = 5, candidates=(0, 1, 2, 4)):
+                                        eps: float = 1e-6, out: torch.Tensor = None, iters: int = 10, candidates=(0, 1, 2, 4)):
     """Times :func:`allreduce_residual_rmsnorm` on these tensors under each shape of its switch path (CUDA
     events, summed over the ranks so that every rank takes the same decision), keeps the fastest on this
-    communicator and returns ``{rows: microseconds averaged over ranks}``.  ``residual`` is used as scratch
-    output.  Collective; a no-op without an NVSwitch multicast alias or on one rank."""
+    communicator and returns ``{rows: microseconds averaged over ranks}``.  The runs update ``residual`` in
+    place (as a layer stack does), so its content is not preserved.  Collective; a no-op without an NVSwitch
+    multicast alias or on one rank."""
     if comm.world_size == 1 or not comm.info["nvls"]:
         return {}
     if out is None:
         out = torch.empty_like(x)
-    scratch = torch.empty_like(residual)
     stream = torch.cuda.current_stream(x.device)
     times = torch.zeros(len(candidates), device=x.device, dtype=torch.float32)
+    tick = torch.zeros(1, device=x.device)
     for i, rows in enumerate(candidates):
         comm.set_fused_norm_rows(rows)
-        allreduce_residual_rmsnorm(comm, x, residual, gamma, eps, out=out, residual_out=scratch)  # warm-up
+        allreduce_residual_rmsnorm(comm, x, residual, gamma, eps, out=out, residual_out=residual)  # warm-up
+        # line the ranks' hosts up, so that the timed launches are not spent waiting for a late peer
+        comm.allreduce(tick)
+        stream.synchronize()
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s.record(stream)
         for _ in range(iters):
-            allreduce_residual_rmsnorm(comm, x, residual, gamma, eps, out=out, residual_out=scratch)
+            allreduce_residual_rmsnorm(comm, x, residual, gamma, eps, out=out, residual_out=residual)
         e.record(stream)
         e.synchronize()
         times[i] = s.elapsed_time(e) * 1e3 / iters
