@@ -48,8 +48,7 @@ class TensorParallelMLP:
     __call__ = forward
 
     # candidates of autotune(): (all-gather mode, communication CTAs or copy-engine lanes, chunks per peer)
-    # "ce" with 32 + k communication CTAs: k copy-engine lanes and a stream of its own for the arrival flags
-    AG_CANDIDATES = (("ce", 0, 2), ("ce", 1, 2), ("ce", 1, 4), ("ce", 33, 2),
+    AG_CANDIDATES = (("ce", 0, 2), ("ce", 1, 2), ("ce", 1, 4), ("ce", 2, 2),
                      ("spread", 0, 0), ("kernel", 8, 0), ("kernel", 16, 0))
 
     def _align(self, stream):
