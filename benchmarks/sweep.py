@@ -155,6 +155,8 @@ def main():
                             if algo == "copy_engine" and nbytes < (1 << 20):
                                 continue
                             uccl_algo(coll, "allgather", algo, "simple", dtn, nbytes, lambda: comm.allgather(small, big_sym), it, busf)
+                        if cnt * es <= 65536:  # low-latency packets: up to 64 KiB per rank
+                            uccl_algo(coll, "allgather", "one_shot", "ll", dtn, nbytes, lambda: comm.allgather(small, big_sym), it, busf)
                         if args.unregistered:
                             comm.set_algo("auto", "auto")
                             record(coll, "uccl", "auto", "auto", dtn, nbytes, timed(lambda: comm.allgather(small, big), it), busf, False)
@@ -164,6 +166,8 @@ def main():
                             if algo == "copy_engine" and nbytes < (1 << 20):
                                 continue
                             uccl_algo(coll, "reducescatter", algo, "simple", dtn, nbytes, lambda: comm.reduce_scatter(big_sym, small), it, busf)
+                        if cnt * es <= 65536:
+                            uccl_algo(coll, "reducescatter", "one_shot", "ll", dtn, nbytes, lambda: comm.reduce_scatter(big_sym, small), it, busf)
                         if args.unregistered:
                             comm.set_algo("auto", "auto")
                             record(coll, "uccl", "auto", "auto", dtn, nbytes, timed(lambda: comm.reduce_scatter(big, small), it), busf, False)

@@ -295,10 +295,13 @@ bool Tuner::feasible(const TuneQuery& q, ucclAlgo_t algo, ucclProto_t proto) {
   const bool reduces = q.coll == ucclCollAllReduce || q.coll == ucclCollReduceScatter || q.coll == ucclCollReduce;
   if (reduces && !q.reducible) return false;
   if (proto == ucclProtoLL || proto == ucclProtoLL128) {
-    // low-latency protocols: all-reduce only, bounded by the per-CTA LL capacity
-    if (q.coll != ucclCollAllReduce) return false;
+    // low-latency protocols: bounded by the per-CTA LL capacity (per message for the all-reduce,
+    // per rank chunk for all-gather and reduce-scatter, whose packets exist in the LL form only)
+    const bool chunked = q.coll == ucclCollAllGather || q.coll == ucclCollReduceScatter;
+    if (q.coll != ucclCollAllReduce && !(chunked && proto == ucclProtoLL && algo == ucclAlgoOneShot)) return false;
     if (algo != ucclAlgoOneShot && algo != ucclAlgoRing) return false;
-    if (q.bytes > static_cast<size_t>(kLLBlocks) * kLLDataPerBlock) return false;
+    const size_t unit = chunked ? q.bytes / static_cast<size_t>(std::max(q.nranks, 1)) : q.bytes;
+    if (unit > static_cast<size_t>(kLLBlocks) * kLLDataPerBlock) return false;
   }
   if (algo == ucclAlgoRing &&
       !(q.coll == ucclCollAllReduce || q.coll == ucclCollAllGather || q.coll == ucclCollReduceScatter))
@@ -357,6 +360,17 @@ TuneChoice Tuner::prior(const TuneQuery& q) const {
       break;
     case ucclCollAllGather:
     case ucclCollReduceScatter:
+      // up to 32 KiB per rank the packet form, which needs no barrier at all, wins (2 GPUs: 7 us
+      // against 11-13 us for the barrier kernels and 16-21 us for the library, 1 KiB - 64 KiB)
+      if (q.bytes / static_cast<size_t>(std::max(q.nranks, 1)) <= (32u << 10) && feasible(q, ucclAlgoOneShot, ucclProtoLL)) {
+        c.algo = ucclAlgoOneShot;
+        c.proto = ucclProtoLL;
+        const size_t chunk = q.bytes / static_cast<size_t>(std::max(q.nranks, 1));
+        c.blocks = static_cast<int>(std::min<size_t>(kLLBlocks, std::max<size_t>(1, (chunk + kLLDataPerBlock - 1) / kLLDataPerBlock)));
+        break;
+      }
+      c.algo = (nvls && q.bytes > (64u << 10)) ? ucclAlgoNvls : ucclAlgoTwoShot;
+      break;
     case ucclCollBroadcast:
     case ucclCollReduce:
       c.algo = (nvls && q.bytes > (64u << 10)) ? ucclAlgoNvls : ucclAlgoTwoShot;
@@ -395,6 +409,20 @@ TuneChoice Tuner::choose(const TuneQuery& q) const {
       best.proto = cv.proto;
       if (blocks > 0) best.blocks = blocks;
       best.fromTable = true;
+    }
+  }
+  // a table measured before an algorithm existed does not veto it: the packet form of all-gather /
+  // reduce-scatter takes its prior unless the table has a curve for it
+  if (found && !algoForced && !protoForced && (q.coll == ucclCollAllGather || q.coll == ucclCollReduceScatter)) {
+    const TuneChoice p = prior(q);
+    if (p.proto == ucclProtoLL) {
+      bool hasCurve = false;
+      for (const TuneCurve& cv : curves_)
+        if (cv.coll == q.coll && cv.proto == ucclProtoLL) hasCurve = true;
+      if (!hasCurve) {
+        best = p;
+        found = true;
+      }
     }
   }
   if (!found) {

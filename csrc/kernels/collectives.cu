@@ -257,6 +257,132 @@ __device__ void ar_ll(const CollArgs& a) {
   if (t == 0) dc.llEpochs[b] = e;
 }
 
+// ------------------------------------------------------------------ all-gather / reduce-scatter, low latency
+// The packet scheme of ar_ll for the two chunked collectives, same slots and epochs: a.bytes is the
+// size of one rank's chunk (at most kLLBlocks * kLLDataPerBlock), CTA b and thread t own the same
+// 8 bytes of every chunk.
+//   reduce-scatter: the unit of chunk p goes to rank p; a rank adds the n - 1 units it receives to
+//                   its own (fp32) and stores the result.
+//   all-gather:     the unit of my chunk goes to every peer; a rank stores the n - 1 units it
+//                   receives next to its own.  Bytes only, no element type.
+// Every rank sends to every peer and waits for every peer in both, so the rule that makes the
+// double-buffered slots safe holds as for the all-reduce: nobody can be more than one operation ahead.
+__device__ __forceinline__ void ll_load_unit(const char* p, int nbytes, uint32_t& w0, uint32_t& w1) {
+  if (nbytes == 8 && (reinterpret_cast<uintptr_t>(p) & 7) == 0) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    w0 = v.x;
+    w1 = v.y;
+    return;
+  }
+  uint32_t w[2] = {0u, 0u};
+  for (int j = 0; j < nbytes; ++j) w[j >> 2] |= static_cast<uint32_t>(static_cast<unsigned char>(p[j])) << (8 * (j & 3));
+  w0 = w[0];
+  w1 = w[1];
+}
+__device__ __forceinline__ void ll_store_unit(char* p, int nbytes, uint32_t w0, uint32_t w1) {
+  if (nbytes == 8 && (reinterpret_cast<uintptr_t>(p) & 7) == 0) {
+    *reinterpret_cast<uint2*>(p) = make_uint2(w0, w1);
+    return;
+  }
+  const uint32_t w[2] = {w0, w1};
+  for (int j = 0; j < nbytes; ++j) p[j] = static_cast<char>(w[j >> 2] >> (8 * (j & 3)));
+}
+template <int DT>
+__device__ __forceinline__ void ll_accumulate(float (&acc)[4], uint32_t w0, uint32_t w1) {
+  if (DT == DT_F32) {
+    acc[0] += __uint_as_float(w0);
+    acc[1] += __uint_as_float(w1);
+  } else if (DT == DT_BF16) {
+    const float2 f0 = ptx::unpack_bf16x2(w0), f1 = ptx::unpack_bf16x2(w1);
+    acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
+  } else {
+    const float2 f0 = ptx::unpack_f16x2(w0), f1 = ptx::unpack_f16x2(w1);
+    acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
+  }
+}
+// waits for the packet of epoch e in `slot`; false on abort or when the time is up
+__device__ __forceinline__ bool ll_wait_packet(const DevComm& dc, const char* slot, uint32_t e, int peer, uint64_t t0, uint4* pkt) {
+  uint32_t spins = 0;
+  while (true) {
+    *pkt = ptx::ld_volatile_v4(slot);
+    if (pkt->y == e && pkt->w == e) return true;
+    if ((++spins & 63u) == 0) {
+      if (aborted(dc)) return false;
+      if (ptx::globaltimer_ns() - t0 > dc.timeoutNs) {
+        record_status(dc, DEV_TIMEOUT_LL, peer, e);
+        return false;
+      }
+    }
+  }
+}
+
+template <int DT, bool GATHER>
+__device__ void chunk_ll(const CollArgs& a) {
+  const DevComm& dc = a.dc;
+  const int b = blockIdx.x, n = dc.nranks, t = threadIdx.x, me = dc.rank;
+  const uint32_t e = dc.llEpochs[b] + 1;
+  const int parity = e & 1;
+  const size_t base = static_cast<size_t>(b) * kLLDataPerBlock;
+  const size_t valid = a.bytes > base ? min(static_cast<size_t>(kLLDataPerBlock), a.bytes - base) : 0;
+  const size_t unitOff = static_cast<size_t>(t) * 8;
+  if (unitOff < valid) {
+    const int nb = static_cast<int>(min(static_cast<size_t>(8), valid - unitOff));
+    const size_t off = base + unitOff;
+    const size_t slotBase = kArenaLLOff + (static_cast<size_t>(parity) * kLLBlocks + b) * UCCL_MAX_LOCAL_RANKS * kLLSlotBytes +
+                            static_cast<size_t>(t) * 16;
+    // send
+    uint32_t m0, m1;  // my own unit: of my chunk (gather) or of chunk `me` of my input (reduce-scatter)
+    if (GATHER) {
+      ll_load_unit(a.inUser + off, nb, m0, m1);
+      const uint4 pkt = make_uint4(m0, e, m1, e);
+      for (int q = 1; q < n; ++q)
+        ptx::st_volatile_v4(dc.arena[(me + q) % n] + slotBase + static_cast<size_t>(me) * kLLSlotBytes, pkt);
+    } else {
+      for (int q = 1; q < n; ++q) {
+        const int p = (me + q) % n;
+        uint32_t w0, w1;
+        ll_load_unit(a.inUser + static_cast<size_t>(p) * a.inStride + off, nb, w0, w1);
+        ptx::st_volatile_v4(dc.arena[p] + slotBase + static_cast<size_t>(me) * kLLSlotBytes, make_uint4(w0, e, w1, e));
+      }
+      ll_load_unit(a.inUser + static_cast<size_t>(me) * a.inStride + off, nb, m0, m1);
+    }
+    // receive
+    const uint64_t t0 = ptx::globaltimer_ns();
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    if (GATHER) {
+      char* own = a.outUser + static_cast<size_t>(me) * a.outStride + off;
+      if (own != a.inUser + off) ll_store_unit(own, nb, m0, m1);
+    } else {
+      ll_accumulate<DT>(acc, m0, m1);
+    }
+    bool ok = true;
+    for (int q = 1; q < n && ok; ++q) {
+      const int p = (me + q) % n;
+      uint4 pkt;
+      ok = ll_wait_packet(dc, dc.arena[me] + slotBase + static_cast<size_t>(p) * kLLSlotBytes, e, p, t0, &pkt);
+      if (!ok) break;
+      if (GATHER) ll_store_unit(a.outUser + static_cast<size_t>(p) * a.outStride + off, nb, pkt.x, pkt.z);
+      else ll_accumulate<DT>(acc, pkt.x, pkt.z);
+    }
+    if (ok && !GATHER) {
+      uint32_t w0, w1;
+      if (DT == DT_F32) {
+        w0 = __float_as_uint(acc[0]);
+        w1 = __float_as_uint(acc[1]);
+      } else if (DT == DT_BF16) {
+        w0 = ptx::pack_bf16x2(acc[0], acc[1]);
+        w1 = ptx::pack_bf16x2(acc[2], acc[3]);
+      } else {
+        w0 = ptx::pack_f16x2(acc[0], acc[1]);
+        w1 = ptx::pack_f16x2(acc[2], acc[3]);
+      }
+      ll_store_unit(a.outUser + off, nb, w0, w1);
+    }
+  }
+  __syncthreads();
+  if (t == 0) dc.llEpochs[b] = e;
+}
+
 // ------------------------------------------------------------------ all-gather
 // pull: every rank reads each peer's chunk straight into its own output
 __device__ void ag_pull(const CollArgs& a) {
@@ -469,6 +595,8 @@ __global__ void __launch_bounds__(kThreads, 1) coll_kernel(const __grid_constant
   if (K == KERN_AR_TWOSHOT) ar_twoshot<DT, false>(a);
   if (K == KERN_AR_NVLS) ar_twoshot<DT, true>(a);
   if (K == KERN_AR_LL) ar_ll<DT>(a);
+  if (K == KERN_RS_LL) chunk_ll<DT, false>(a);
+  if (K == KERN_AG_LL) chunk_ll<DT, true>(a);
   if (K == KERN_AG_PULL) ag_pull(a);
   if (K == KERN_AG_PUSH) ag_push(a);
   if (K == KERN_RS_PULL) rs_pull<DT>(a);
@@ -514,6 +642,8 @@ cudaError_t launchCollKernel(CollKernel k, const CollArgs& a, int blocks, cudaSt
     case KERN_A2A_PULL: return launchUntyped<KERN_A2A_PULL>(a, blocks, stream);
     case KERN_BARRIER: return launchUntyped<KERN_BARRIER>(a, 1, stream);
     case KERN_LOCAL_REDUCE: return launchTyped<KERN_LOCAL_REDUCE>(a, blocks, stream);
+    case KERN_RS_LL: return blocks <= kLLBlocks ? launchTyped<KERN_RS_LL>(a, blocks, stream) : cudaErrorInvalidValue;
+    case KERN_AG_LL: return blocks <= kLLBlocks ? launchUntyped<KERN_AG_LL>(a, blocks, stream) : cudaErrorInvalidValue;
   }
   return cudaErrorInvalidValue;
 }

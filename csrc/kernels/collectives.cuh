@@ -44,6 +44,8 @@ enum CollKernel : int {
   KERN_A2A_PULL = 10,
   KERN_BARRIER = 11,       // a rank barrier and nothing else (copy-engine mode)
   KERN_LOCAL_REDUCE = 12,  // out[0] = sum of `root` local slots of in[0], inStride apart
+  KERN_RS_LL = 13,         // low-latency packets: inUser = [nranks][bytes] (inStride apart), outUser = my reduced chunk
+  KERN_AG_LL = 14,         // low-latency packets: inUser = my chunk, outUser = [nranks][bytes] (outStride apart)
 };
 
 cudaError_t launchCollKernel(CollKernel k, const CollArgs& a, int blocks, cudaStream_t stream);

@@ -176,13 +176,14 @@ def case_allreduce_algos(comm, rank, n, args):
 
 
 def case_ring_ce_matrix(comm, rank, n, args):
-    """All-gather, reduce-scatter and all-reduce forced onto the ring (Simple and LL128) and onto the
-    copy engines, out of place and in place.  Run with a small UCCL_STAGING_BYTES and few CTAs so that
+    """All-gather, reduce-scatter and all-reduce forced onto the ring (Simple and LL128), onto the
+    copy engines and onto the low-latency packets, out of place and in place.  Run with a small UCCL_STAGING_BYTES and few CTAs so that
     one chunk needs more pieces than a channel has slots (several rounds of the reduce-scatter
     schedule, FIFO wrap-around) and the copy-engine path loops over its staging area."""
     dev = _dev(comm, rank)
     fail = []
-    combos = [("ring", "simple"), ("ring", "ll128"), ("copy_engine", "simple")]
+    # one_shot / ll: the packet form of all three (chunks up to 64 KiB; larger ones take the direct kernels)
+    combos = [("ring", "simple"), ("ring", "ll128"), ("copy_engine", "simple"), ("one_shot", "ll")]
     for dt in (torch.float32, torch.bfloat16):
         tol = {torch.float32: 1e-5, torch.bfloat16: 2e-2}[dt] * n
         for cnt in (5, 4099, (1 << 20) + 3):
