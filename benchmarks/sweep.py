@@ -194,6 +194,8 @@ def main():
                     src = torch.ones(cnt * n, dtype=dt, device=dev)
                     record(coll, "nccl", "nccl", "-", dtn, nbytes, timed(lambda: dist.all_to_all_single(dst, src), it), (n - 1) / n, False)
                     uccl_algo(coll, "alltoall", "two_shot", "simple", dtn, nbytes, lambda: comm.alltoall(sym, dst), it, (n - 1) / n)
+                    if cnt * es <= 65536:  # low-latency packets: up to 64 KiB per rank
+                        uccl_algo(coll, "alltoall", "one_shot", "ll", dtn, nbytes, lambda: comm.alltoall(sym, dst), it, (n - 1) / n)
                     comm.set_algo("auto", "auto")
                     record(coll, "uccl", "auto", "auto", dtn, nbytes, timed(lambda: comm.alltoall(sym, dst), it), (n - 1) / n, True)
                     comm.free(sym)

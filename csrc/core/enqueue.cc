@@ -104,15 +104,15 @@ ucclResult_t arLL(Comm* c, const CollOp& op, size_t bytes) {
 }
 
 // all-gather / reduce-scatter as low-latency packets straight between the user buffers (see chunk_ll)
-ucclResult_t chunkLL(Comm* c, const CollOp& op, size_t chunk, bool gather) {
+ucclResult_t chunkLL(Comm* c, const CollOp& op, size_t chunk, CollKernel kern) {
   CollArgs a;
-  baseArgs(c, &a, gather ? ucclFloat32 : op.dtype);  // the gather moves bytes, whatever the element type
+  baseArgs(c, &a, kern == KERN_RS_LL ? op.dtype : ucclFloat32);  // gather and all-to-all move bytes, whatever the element type
   a.inUser = static_cast<const char*>(op.send);
   a.outUser = static_cast<char*>(op.recv);
   a.bytes = a.userBytes = chunk;
   a.inStride = a.outStride = chunk;
   const int blocks = std::max(1, static_cast<int>((chunk + kLLDataPerBlock - 1) / kLLDataPerBlock));
-  return launch(c, gather ? KERN_AG_LL : KERN_RS_LL, a, blocks, op.stream);
+  return launch(c, kern, a, blocks, op.stream);
 }
 
 ucclResult_t arDirect(Comm* c, const CollOp& op, size_t bytes, const TuneChoice& ch) {
@@ -528,15 +528,17 @@ ucclResult_t executeOp(const CollOp& op) {
         return arLL(c, op, chunk);
       return arDirect(c, op, chunk, ch);
     case ucclCollAllGather:
-      if (ch.proto == ucclProtoLL && chunk <= static_cast<size_t>(kLLBlocks) * kLLDataPerBlock) return chunkLL(c, op, chunk, true);
+      if (ch.proto == ucclProtoLL && chunk <= static_cast<size_t>(kLLBlocks) * kLLDataPerBlock) return chunkLL(c, op, chunk, KERN_AG_LL);
       return agDirect(c, op, chunk, ch);
     case ucclCollReduceScatter:
       if (ch.proto == ucclProtoLL && chunk <= static_cast<size_t>(kLLBlocks) * kLLDataPerBlock && reducible(op.dtype))
-        return chunkLL(c, op, chunk, false);
+        return chunkLL(c, op, chunk, KERN_RS_LL);
       return rsDirect(c, op, chunk, ch);
     case ucclCollBroadcast: return bcastDirect(c, op, chunk, ch);
     case ucclCollReduce: return reduceDirect(c, op, chunk, ch);
-    case ucclCollAllToAll: return a2aDirect(c, op, chunk, ch);
+    case ucclCollAllToAll:
+      if (ch.proto == ucclProtoLL && chunk <= static_cast<size_t>(kLLBlocks) * kLLDataPerBlock) return chunkLL(c, op, chunk, KERN_A2A_LL);
+      return a2aDirect(c, op, chunk, ch);
     case ucclCollSendRecv: {
       std::vector<CollOp> v(1, op);
       return executeP2pBatch(c, v);

@@ -297,7 +297,7 @@ bool Tuner::feasible(const TuneQuery& q, ucclAlgo_t algo, ucclProto_t proto) {
   if (proto == ucclProtoLL || proto == ucclProtoLL128) {
     // low-latency protocols: bounded by the per-CTA LL capacity (per message for the all-reduce,
     // per rank chunk for all-gather and reduce-scatter, whose packets exist in the LL form only)
-    const bool chunked = q.coll == ucclCollAllGather || q.coll == ucclCollReduceScatter;
+    const bool chunked = q.coll == ucclCollAllGather || q.coll == ucclCollReduceScatter || q.coll == ucclCollAllToAll;
     if (q.coll != ucclCollAllReduce && !(chunked && proto == ucclProtoLL && algo == ucclAlgoOneShot)) return false;
     if (algo != ucclAlgoOneShot && algo != ucclAlgoRing) return false;
     const size_t unit = chunked ? q.bytes / static_cast<size_t>(std::max(q.nranks, 1)) : q.bytes;
@@ -377,6 +377,13 @@ TuneChoice Tuner::prior(const TuneQuery& q) const {
       if (q.coll == ucclCollReduce && !nvls) c.algo = ucclAlgoOneShot;
       break;
     case ucclCollAllToAll:
+      if (q.bytes / static_cast<size_t>(std::max(q.nranks, 1)) <= (32u << 10) && feasible(q, ucclAlgoOneShot, ucclProtoLL)) {
+        c.algo = ucclAlgoOneShot;
+        c.proto = ucclProtoLL;
+        const size_t chunk = q.bytes / static_cast<size_t>(std::max(q.nranks, 1));
+        c.blocks = static_cast<int>(std::min<size_t>(kLLBlocks, std::max<size_t>(1, (chunk + kLLDataPerBlock - 1) / kLLDataPerBlock)));
+        break;
+      }
       // pure copies, nothing to reduce: one CTA per 128 KiB of the message
       c.algo = ucclAlgoTwoShot;
       c.blocks = static_cast<int>(std::min<size_t>(48, std::max<size_t>(c.blocks, q.bytes >> 17)));
@@ -413,7 +420,8 @@ TuneChoice Tuner::choose(const TuneQuery& q) const {
   }
   // a table measured before an algorithm existed does not veto it: the packet form of all-gather /
   // reduce-scatter takes its prior unless the table has a curve for it
-  if (found && !algoForced && !protoForced && (q.coll == ucclCollAllGather || q.coll == ucclCollReduceScatter)) {
+  if (found && !algoForced && !protoForced &&
+      (q.coll == ucclCollAllGather || q.coll == ucclCollReduceScatter || q.coll == ucclCollAllToAll)) {
     const TuneChoice p = prior(q);
     if (p.proto == ucclProtoLL) {
       bool hasCurve = false;

@@ -265,6 +265,7 @@ __device__ void ar_ll(const CollArgs& a) {
 //                   its own (fp32) and stores the result.
 //   all-gather:     the unit of my chunk goes to every peer; a rank stores the n - 1 units it
 //                   receives next to its own.  Bytes only, no element type.
+//   all-to-all:     the unit of chunk p goes to rank p, which stores it as chunk [sender] of its output.
 // Every rank sends to every peer and waits for every peer in both, so the rule that makes the
 // double-buffered slots safe holds as for the all-reduce: nobody can be more than one operation ahead.
 __device__ __forceinline__ void ll_load_unit(const char* p, int nbytes, uint32_t& w0, uint32_t& w1) {
@@ -316,8 +317,11 @@ __device__ __forceinline__ bool ll_wait_packet(const DevComm& dc, const char* sl
   }
 }
 
-template <int DT, bool GATHER>
+enum : int { LL_REDUCE_SCATTER = 0, LL_ALLGATHER = 1, LL_ALLTOALL = 2 };
+template <int DT, int MODE>
 __device__ void chunk_ll(const CollArgs& a) {
+  constexpr bool GATHER = MODE == LL_ALLGATHER;
+  constexpr bool REDUCE = MODE == LL_REDUCE_SCATTER;
   const DevComm& dc = a.dc;
   const int b = blockIdx.x, n = dc.nranks, t = threadIdx.x, me = dc.rank;
   const uint32_t e = dc.llEpochs[b] + 1;
@@ -331,7 +335,7 @@ __device__ void chunk_ll(const CollArgs& a) {
     const size_t slotBase = kArenaLLOff + (static_cast<size_t>(parity) * kLLBlocks + b) * UCCL_MAX_LOCAL_RANKS * kLLSlotBytes +
                             static_cast<size_t>(t) * 16;
     // send
-    uint32_t m0, m1;  // my own unit: of my chunk (gather) or of chunk `me` of my input (reduce-scatter)
+    uint32_t m0, m1;  // my own unit: of my chunk (gather) or of chunk `me` of my input (reduce-scatter, all-to-all)
     if (GATHER) {
       ll_load_unit(a.inUser + off, nb, m0, m1);
       const uint4 pkt = make_uint4(m0, e, m1, e);
@@ -349,11 +353,11 @@ __device__ void chunk_ll(const CollArgs& a) {
     // receive
     const uint64_t t0 = ptx::globaltimer_ns();
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    if (GATHER) {
-      char* own = a.outUser + static_cast<size_t>(me) * a.outStride + off;
-      if (own != a.inUser + off) ll_store_unit(own, nb, m0, m1);
-    } else {
+    if (REDUCE) {
       ll_accumulate<DT>(acc, m0, m1);
+    } else {
+      char* own = a.outUser + static_cast<size_t>(me) * a.outStride + off;
+      if (own != a.inUser + (GATHER ? 0 : static_cast<size_t>(me) * a.inStride) + off) ll_store_unit(own, nb, m0, m1);
     }
     bool ok = true;
     for (int q = 1; q < n && ok; ++q) {
@@ -361,10 +365,10 @@ __device__ void chunk_ll(const CollArgs& a) {
       uint4 pkt;
       ok = ll_wait_packet(dc, dc.arena[me] + slotBase + static_cast<size_t>(p) * kLLSlotBytes, e, p, t0, &pkt);
       if (!ok) break;
-      if (GATHER) ll_store_unit(a.outUser + static_cast<size_t>(p) * a.outStride + off, nb, pkt.x, pkt.z);
-      else ll_accumulate<DT>(acc, pkt.x, pkt.z);
+      if (REDUCE) ll_accumulate<DT>(acc, pkt.x, pkt.z);
+      else ll_store_unit(a.outUser + static_cast<size_t>(p) * a.outStride + off, nb, pkt.x, pkt.z);
     }
-    if (ok && !GATHER) {
+    if (ok && REDUCE) {
       uint32_t w0, w1;
       if (DT == DT_F32) {
         w0 = __float_as_uint(acc[0]);
@@ -595,8 +599,9 @@ __global__ void __launch_bounds__(kThreads, 1) coll_kernel(const __grid_constant
   if (K == KERN_AR_TWOSHOT) ar_twoshot<DT, false>(a);
   if (K == KERN_AR_NVLS) ar_twoshot<DT, true>(a);
   if (K == KERN_AR_LL) ar_ll<DT>(a);
-  if (K == KERN_RS_LL) chunk_ll<DT, false>(a);
-  if (K == KERN_AG_LL) chunk_ll<DT, true>(a);
+  if (K == KERN_RS_LL) chunk_ll<DT, LL_REDUCE_SCATTER>(a);
+  if (K == KERN_AG_LL) chunk_ll<DT, LL_ALLGATHER>(a);
+  if (K == KERN_A2A_LL) chunk_ll<DT, LL_ALLTOALL>(a);
   if (K == KERN_AG_PULL) ag_pull(a);
   if (K == KERN_AG_PUSH) ag_push(a);
   if (K == KERN_RS_PULL) rs_pull<DT>(a);
@@ -644,6 +649,7 @@ cudaError_t launchCollKernel(CollKernel k, const CollArgs& a, int blocks, cudaSt
     case KERN_LOCAL_REDUCE: return launchTyped<KERN_LOCAL_REDUCE>(a, blocks, stream);
     case KERN_RS_LL: return blocks <= kLLBlocks ? launchTyped<KERN_RS_LL>(a, blocks, stream) : cudaErrorInvalidValue;
     case KERN_AG_LL: return blocks <= kLLBlocks ? launchUntyped<KERN_AG_LL>(a, blocks, stream) : cudaErrorInvalidValue;
+    case KERN_A2A_LL: return blocks <= kLLBlocks ? launchUntyped<KERN_A2A_LL>(a, blocks, stream) : cudaErrorInvalidValue;
   }
   return cudaErrorInvalidValue;
 }

@@ -46,6 +46,7 @@ enum CollKernel : int {
   KERN_LOCAL_REDUCE = 12,  // out[0] = sum of `root` local slots of in[0], inStride apart
   KERN_RS_LL = 13,         // low-latency packets: inUser = [nranks][bytes] (inStride apart), outUser = my reduced chunk
   KERN_AG_LL = 14,         // low-latency packets: inUser = my chunk, outUser = [nranks][bytes] (outStride apart)
+  KERN_A2A_LL = 15,        // low-latency packets: inUser and outUser = [nranks][bytes]
 };
 
 cudaError_t launchCollKernel(CollKernel k, const CollArgs& a, int blocks, cudaStream_t stream);
