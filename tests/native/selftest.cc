@@ -410,6 +410,44 @@ std::string testTuner() {
   q.coll = ucclCollAllGather;
   EXPECT(Tuner::feasible(q, ucclAlgoTwoShot, ucclProtoSimple));
   EXPECT(!Tuner::feasible(q, ucclAlgoOneShot, ucclProtoLL));
+  // the packet form of the chunked collectives: feasible up to 64 KiB per rank, the prior up to 32 KiB,
+  // and a table that was measured without it does not veto it
+  {
+    TuneQuery g;
+    g.coll = ucclCollAllGather;
+    g.nranks = 8;
+    g.nvls = true;
+    g.bytes = 8u * (64u << 10);
+    EXPECT(Tuner::feasible(g, ucclAlgoOneShot, ucclProtoLL));
+    g.bytes += 8;
+    EXPECT(!Tuner::feasible(g, ucclAlgoOneShot, ucclProtoLL));
+    Tuner u;
+    g.bytes = 8u * 4096u;
+    TuneChoice k = u.choose(g);
+    EXPECT(k.algo == ucclAlgoOneShot && k.proto == ucclProtoLL && k.blocks == 1);
+    g.bytes = 8u * (48u << 10);
+    k = u.choose(g);
+    EXPECT(k.proto == ucclProtoSimple);
+    std::string w;
+    EXPECT(u.loadText("{\"version\":1,\"nranks\":8,\"entries\":["
+                      "{\"coll\":\"allgather\",\"algo\":\"two_shot\",\"proto\":\"simple\",\"bytes\":1024,\"us\":12.0,\"blocks\":1},"
+                      "{\"coll\":\"allgather\",\"algo\":\"two_shot\",\"proto\":\"simple\",\"bytes\":1048576,\"us\":20.0,\"blocks\":8}]}", &w));
+    g.bytes = 8u * 4096u;
+    k = u.choose(g);
+    EXPECT(k.algo == ucclAlgoOneShot && k.proto == ucclProtoLL);  // no curve for it in the table: the prior stands
+    EXPECT(u.loadText("{\"version\":1,\"nranks\":8,\"entries\":["
+                      "{\"coll\":\"allgather\",\"algo\":\"two_shot\",\"proto\":\"simple\",\"bytes\":1024,\"us\":12.0,\"blocks\":1},"
+                      "{\"coll\":\"allgather\",\"algo\":\"two_shot\",\"proto\":\"simple\",\"bytes\":1048576,\"us\":20.0,\"blocks\":8},"
+                      "{\"coll\":\"allgather\",\"algo\":\"one_shot\",\"proto\":\"ll\",\"bytes\":1024,\"us\":30.0,\"blocks\":1},"
+                      "{\"coll\":\"allgather\",\"algo\":\"one_shot\",\"proto\":\"ll\",\"bytes\":65536,\"us\":40.0,\"blocks\":2}]}", &w));
+    k = u.choose(g);
+    EXPECT(k.fromTable && k.algo == ucclAlgoTwoShot);  // measured slower here: the table decides
+    g.coll = ucclCollAllToAll;
+    g.bytes = 8u * 1024u;
+    Tuner v;
+    k = v.choose(g);
+    EXPECT(k.algo == ucclAlgoOneShot && k.proto == ucclProtoLL);
+  }
   return "";
 }
 
