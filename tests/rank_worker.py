@@ -183,7 +183,10 @@ def case_ring_ce_matrix(comm, rank, n, args):
     dev = _dev(comm, rank)
     fail = []
     # one_shot / ll: the packet form of all three (chunks up to 64 KiB; larger ones take the direct kernels)
-    combos = [("ring", "simple"), ("ring", "ll128"), ("copy_engine", "simple"), ("one_shot", "ll")]
+    # two_shot / one_shot: the direct kernels, which with this staging area move a few MiB of ordinary
+    # (not symmetric) memory in several pieces
+    combos = [("ring", "simple"), ("ring", "ll128"), ("copy_engine", "simple"), ("one_shot", "ll"),
+              ("two_shot", "simple"), ("one_shot", "simple")]
     for dt in (torch.float32, torch.bfloat16):
         tol = {torch.float32: 1e-5, torch.bfloat16: 2e-2}[dt] * n
         for cnt in (5, 4099, (1 << 20) + 3):

@@ -48,6 +48,19 @@ def test_ring_and_copy_engine_allgather_reduce_scatter():
     assert res[0]["algo_hist"][1] > 0 and res[0]["algo_hist"][5] > 0
 
 
+def test_hybrid_exec_mode():
+    """UCCL_EXEC_MODE=hybrid: SM kernels below 1 MiB, copy engines from there up."""
+    res = run_ranks("collectives_symmetric", _n(), env={"UCCL_EXEC_MODE": "hybrid"}, timeout=300)
+    assert_all_ok(res)
+
+
+def test_cuda_ipc_heap():
+    """UCCL_P2P=ipc: the symmetric heap from cudaMalloc + cudaIpc handles (no multicast) instead of VMM."""
+    res = run_ranks("collectives_symmetric", 2, env={"UCCL_P2P": "ipc"}, timeout=300)
+    assert_all_ok(res)
+    assert not res[0]["nvls"]
+
+
 def test_collectives_with_scale_and_cast():
     """ucclReduceScatterEx / ucclAllReduceEx: sum, scale, other output type (fp32 / bf16 / fp16 / fp8 + scales)."""
     env = {"UCCL_STAGING_BYTES": "4M"}
