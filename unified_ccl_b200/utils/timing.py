@@ -52,7 +52,7 @@ class ClockSampler:
     # NVML clocks-event (throttle) reason bits
     REASON_BITS = {"sw_power_cap": 0x4, "hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
 
-    def __init__(self, gpu_index=0, period_ms=5):
+    def __init__(self, gpu_index=0, period_ms=2):
         self.gpu_index, self.period_ms = gpu_index, period_ms
         self.samples, self._proc, self._thread = [], None, None
         self._stop = threading.Event()
@@ -76,6 +76,8 @@ class ClockSampler:
             if handle is None:
                 handle = pynvml.nvmlDeviceGetHandleByIndex(self.gpu_index)
             self._nvml, self._handle = pynvml, handle
+            # constant for the device: read once, so that a sample is two or three NVML calls, not four
+            self._max_sm = pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM)
             return True
         except Exception:  # noqa: BLE001
             self._nvml = None
@@ -84,7 +86,7 @@ class ClockSampler:
     def _nvml_sample(self):
         n, h = self._nvml, self._handle
         sm = n.nvmlDeviceGetClockInfo(h, n.NVML_CLOCK_SM)
-        mx = n.nvmlDeviceGetMaxClockInfo(h, n.NVML_CLOCK_SM)
+        mx = self._max_sm
         try:
             watts = n.nvmlDeviceGetPowerUsage(h) / 1000.0
         except Exception:  # noqa: BLE001
