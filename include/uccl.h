@@ -314,7 +314,7 @@ ucclResult_t ucclCommSetFusedOptions(ucclComm_t comm, int agMode, int commCtas, 
 ucclResult_t ucclCommSetFusedRsReducers(ucclComm_t comm, int reducerCtas);
 /* Fused all-reduce + residual + RMSNorm on the switch path: 1..4 = the kernel first all-reduces the rows
  * (that many rows of every CTA per pass), then normalises all rows from local memory; 0 = one phase,
- * every rank normalises the rows it reduced from registers and multicasts both results; -1 = default (4).
+ * every rank normalises the rows it reduced from registers and multicasts both results; -1 = default (1).
  * UCCL_NORM_MC_ROWS wins. */
 ucclResult_t ucclCommSetFusedNormRows(ucclComm_t comm, int rows);
 
