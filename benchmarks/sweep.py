@@ -131,8 +131,8 @@ def main():
                     for algo, proto in combos:
                         if proto == "ll" and nbytes > 65536:
                             continue
-                        if proto == "ll128" and nbytes > (4 << 20):
-                            continue
+                        if proto == "ll128" and nbytes > 65536:
+                            continue  # the tuner refuses it above the packet capacity and would time its own choice instead
                         if algo == "one_shot" and proto == "simple" and nbytes > (16 << 20):
                             continue
                         if algo == "copy_engine" and nbytes < (1 << 20):
